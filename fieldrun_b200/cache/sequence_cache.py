@@ -6,7 +6,7 @@ The reference allocates, per ``generate`` call and for its single sequence, two
 sequences of unequal, growing lengths share one store, so the store is cut into
 pages: a sequence holds ``ceil(length / 64)`` pages per group and a table maps
 (slot, position // 64) to a page.  Cache lines whose needs are the same (number
-of key/value heads, head size, all keys or a window of them) form a *group* with
+of key/value heads, key and value head sizes, all keys or a window of them) form a *group* with
 a store, a page pool and a table of its own; a windowed group gives a page back
 as soon as every key on it lies outside the window.  What is cached is K after
 norm and rotary and V as projected (src/minimax.rs:262-268).
@@ -36,12 +36,13 @@ class CacheNeed:
     kv_heads: int = 0
     head_dim: int = 0
     window: int | None = None            # None: every earlier key stays visible
+    value_dim: int = 0                   # size of a value head; 0: the keys' head_dim
     state_shape: tuple[int, ...] = ()    # state per sequence; () for none
     state_dtype: str = "float32"         # "float32" | "bfloat16" | "int32"
 
     @property
-    def group_key(self) -> tuple[int, int, int | None] | None:
-        return (self.kv_heads, self.head_dim, self.window) if self.kv_heads else None
+    def group_key(self) -> tuple[int, int, int | None, int] | None:
+        return (self.kv_heads, self.head_dim, self.window, self.value_dim or self.head_dim) if self.kv_heads else None
 
 
 def pages_for(tokens: int) -> int:
@@ -53,7 +54,7 @@ class LineView:
     """What a mixer sees of its cache line."""
 
     keys: torch.Tensor | None            # [num_pages, kv_heads, PAGE_TOKENS, head_dim]
-    values: torch.Tensor | None          # [num_pages, kv_heads, head_dim, PAGE_TOKENS]
+    values: torch.Tensor | None          # [num_pages, kv_heads, value_dim, PAGE_TOKENS]
     page_table: torch.Tensor | None      # int32 [num_slots, max_pages]; -1 where no page is held
     window: int | None
     state: torch.Tensor | None           # [num_slots, *state_shape] in the need's state_dtype
@@ -61,7 +62,7 @@ class LineView:
 
 class _Group:
     def __init__(self, key, lines, num_pages, num_slots, dtype, device, allocate):
-        self.kv_heads, self.head_dim, self.window = key
+        self.kv_heads, self.head_dim, self.window, self.value_dim = key
         self.lines = list(lines)
         self.num_pages = num_pages
         self.pool = IndexPool(num_pages, "page")
@@ -75,7 +76,7 @@ class _Group:
             self.keys = torch.zeros(shape, dtype=dtype, device=device)
             # within a page the values lie transposed, [head_dim, PAGE_TOKENS]: the product P @ V then reads
             # runs of neighbouring keys
-            self.values = torch.zeros(shape[:3] + (self.head_dim, PAGE_TOKENS), dtype=dtype, device=device)
+            self.values = torch.zeros(shape[:3] + (self.value_dim, PAGE_TOKENS), dtype=dtype, device=device)
             self.table_dev = torch.full((num_slots, num_pages), -1, dtype=torch.int32, device=device)
         else:
             self.keys = self.values = self.table_dev = None

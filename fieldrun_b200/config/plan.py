@@ -10,7 +10,7 @@ are parts chosen layer by layer.
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Mapping
+from typing import Any, Mapping, Optional
 
 
 @dataclass(frozen=True)
@@ -26,13 +26,15 @@ class PartSpec:
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """A layer: a block arrangement over a mixer and a feed-forward, each behind its norm."""
+    """A layer: a block arrangement over a mixer and a feed-forward, each with its norm (where the norm
+    sits, before the sublayer or on its output, is the block's business).  A layer without a feed-forward
+    has ``feed_forward`` and ``feed_forward_norm`` None."""
 
     block: str
     mixer: PartSpec
-    feed_forward: PartSpec
+    feed_forward: Optional[PartSpec]
     mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
+    feed_forward_norm: Optional[PartSpec]
 
 
 @dataclass(frozen=True)

@@ -9,7 +9,7 @@ with ``model_type`` prefixes as the fallback.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Callable, Mapping
+from typing import Any, Callable, Mapping, Optional
 
 from .base import ConfigError, ModelConfig, read_config_json
 from .plan import ModelPlan
@@ -21,6 +21,8 @@ class Architecture:
     config_from_dict: Callable[[Mapping[str, Any], str], ModelConfig]
     plan: Callable[[ModelConfig], ModelPlan]
     model_type_prefixes: tuple[str, ...] = ()
+    # for a design that leaves a size to a tensor's shape: (config, {tensor name: shape}) -> the completed config
+    sizes_from_tensors: Optional[Callable[[ModelConfig, Mapping[str, tuple[int, ...]]], ModelConfig]] = None
 
 
 _ARCHITECTURES: dict[str, Architecture] = {}
@@ -45,6 +47,8 @@ def architecture_for(raw: Mapping[str, Any], where: str = "config.json") -> Arch
     """Choose the architecture a config.json names."""
     _load_builtin()
     names = raw.get("architectures")
+    if names is None and isinstance(raw.get("architecture"), str):
+        names = [raw["architecture"]]             # some writers name the one architecture as a plain string
     if isinstance(names, (list, tuple)) and names:
         name = names[0]
         if name in _ARCHITECTURES:
@@ -69,4 +73,12 @@ def architecture_for(raw: Mapping[str, Any], where: str = "config.json") -> Arch
 def load_config(model_dir: str) -> tuple[Architecture, ModelConfig]:
     raw = read_config_json(model_dir)
     arch = architecture_for(raw, where=f"{model_dir}/config.json")
-    return arch, arch.config_from_dict(raw, f"{model_dir}/config.json")
+    config = arch.config_from_dict(raw, f"{model_dir}/config.json")
+    if arch.sizes_from_tensors is not None:
+        from ..weights.safetensors_io import ModelFolder      # the header only: names and shapes
+        folder = ModelFolder(model_dir)
+        try:
+            config = arch.sizes_from_tensors(config, {name: tuple(e.shape) for name, e in folder.entries.items()})
+        finally:
+            folder.close()
+    return arch, config

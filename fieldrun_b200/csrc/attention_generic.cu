@@ -6,19 +6,23 @@
 // (j <= its position, and j > position - window when a window is set), p = exp(s - max) / sum,
 // out = sum_j p_j V_j  (src/minimax.rs:270-281).  Keys that are hidden get weight 0 exactly, which is what
 // the reference's -1e30 amounts to after the exponential.
+// Two things the reference's model does not have are arguments here: a value head of another size than the
+// key head (v_dim), and a bias on the score that grows with the distance, s_j -= slope[h] * (i - j) for the query
+// at position i (a slope per query head; null: none).
 #include "common.cuh"
 
 struct AttnParams {
     const void* q;            // [T, nh, hd]
     const void* k_pages;      // [pages, nkv, PAGE, hd]
-    const void* v_pages;      // [pages, nkv, hd, PAGE]: values lie transposed within a page
+    const void* v_pages;      // [pages, nkv, vd, PAGE]: values lie transposed within a page
+    const float* slopes;      // [nh] or null
     const int* page_table;    // [slots, max_pages]
     const int* tok_pos;       // [T]
     const int* tok_slot;      // [T]
-    void* out;                // [T, nh * hd]
+    void* out;                // [T, nh * vd]
     float scale;
     int window;               // 0: every earlier key
-    int max_pages, num_heads, num_kv_heads, head_dim;
+    int max_pages, num_heads, num_kv_heads, head_dim, v_dim;
 };
 
 #define KEY_BLOCK 32
@@ -27,10 +31,10 @@ struct AttnParams {
 template <typename T>
 __global__ void attention_generic_kernel(AttnParams p) {
     extern __shared__ float sm[];
-    const int hd = p.head_dim;
+    const int hd = p.head_dim, vd = p.v_dim;
     float* k_tile = sm;                                  // [KEY_BLOCK][hd + 1]
-    float* v_tile = k_tile + KEY_BLOCK * (hd + 1);       // [KEY_BLOCK][hd]
-    float* q_rows = v_tile + KEY_BLOCK * hd;             // [warps][hd]
+    float* v_tile = k_tile + KEY_BLOCK * (hd + 1);       // [KEY_BLOCK][vd]
+    float* q_rows = v_tile + KEY_BLOCK * vd;             // [warps][hd]
     const int t = blockIdx.x, g = blockIdx.y;
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
     const int group = p.num_heads / p.num_kv_heads;
@@ -49,6 +53,7 @@ __global__ void attention_generic_kernel(AttnParams p) {
         const int head = g * group + hl;
         if (active)
             for (int d = lane; d < hd; d += 32) q_rows[warp * hd + d] = to_f32<T>(q[((size_t)t * p.num_heads + head) * hd + d]);
+        const float slope = (active && p.slopes) ? p.slopes[head] : 0.f;
         float m = -INFINITY, l = 0.f;
         float acc[8];
 #pragma unroll
@@ -58,16 +63,17 @@ __global__ void attention_generic_kernel(AttnParams p) {
             __syncthreads();
             const int page = table[j0 / FRB_PAGE];
             const size_t head_base = ((size_t)page * p.num_kv_heads + g) * FRB_PAGE * hd;
+            const size_t value_base = ((size_t)page * p.num_kv_heads + g) * FRB_PAGE * vd;
             const int in_page = j0 % FRB_PAGE;
             for (int i = threadIdx.x; i < KEY_BLOCK * hd; i += blockDim.x) {
                 const int r = i / hd, d = i - r * hd;
                 const bool valid = (j0 + r >= lo) && (j0 + r <= hi);
                 k_tile[r * (hd + 1) + d] = valid ? to_f32<T>(k_pages[head_base + (size_t)(in_page + r) * hd + d]) : 0.f;
             }
-            for (int i = threadIdx.x; i < KEY_BLOCK * hd; i += blockDim.x) {
+            for (int i = threadIdx.x; i < KEY_BLOCK * vd; i += blockDim.x) {
                 const int d = i / KEY_BLOCK, r = i - d * KEY_BLOCK;          // keys of one dim are neighbours in memory
                 const bool valid = (j0 + r >= lo) && (j0 + r <= hi);
-                v_tile[r * hd + d] = valid ? to_f32<T>(v_pages[head_base + (size_t)d * FRB_PAGE + in_page + r]) : 0.f;
+                v_tile[r * vd + d] = valid ? to_f32<T>(v_pages[value_base + (size_t)d * FRB_PAGE + in_page + r]) : 0.f;
             }
             __syncthreads();
             if (active) {
@@ -77,7 +83,7 @@ __global__ void attention_generic_kernel(AttnParams p) {
                 const float* qr = q_rows + warp * hd;
                 const float* kr = k_tile + lane * (hd + 1);
                 for (int d = 0; d < hd; ++d) s += qr[d] * kr[d];
-                s = valid ? s * p.scale : -INFINITY;
+                s = valid ? s * p.scale - slope * (float)(pos - j) : -INFINITY;
                 const float m_new = fmaxf(m, warp_max(s));
                 const float corr = expf(m - m_new);
                 const float pj = valid ? expf(s - m_new) : 0.f;
@@ -89,7 +95,7 @@ __global__ void attention_generic_kernel(AttnParams p) {
 #pragma unroll
                     for (int i = 0; i < 8; ++i) {
                         const int d = lane + 32 * i;
-                        if (d < hd) acc[i] += pk * v_tile[kk * hd + d];
+                        if (d < vd) acc[i] += pk * v_tile[kk * vd + d];
                     }
                 }
                 m = m_new;
@@ -100,7 +106,7 @@ __global__ void attention_generic_kernel(AttnParams p) {
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int d = lane + 32 * i;
-                if (d < hd) out[((size_t)t * p.num_heads + head) * hd + d] = from_f32<T>(acc[i] * inv);
+                if (d < vd) out[((size_t)t * p.num_heads + head) * vd + d] = from_f32<T>(acc[i] * inv);
             }
         }
     }
@@ -109,8 +115,10 @@ __global__ void attention_generic_kernel(AttnParams p) {
 FRB_API int frb_attention_generic(const void* q, const void* k_pages, const void* v_pages, int dtype,
                                   const int* page_table, int max_pages, const int* tok_pos, const int* tok_slot,
                                   void* out, int num_tokens, int num_heads, int num_kv_heads, int head_dim,
-                                  float scale, int window, cudaStream_t stream) {
+                                  float scale, int window, int v_dim, const float* slopes, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
+    if (v_dim <= 0) v_dim = head_dim;
+    FRB_CHECK_ARG(v_dim <= 256, "attention: v_dim %d is outside 1..256", v_dim);
     FRB_CHECK_ARG(head_dim >= 1 && head_dim <= 256, "attention: head_dim %d is outside 1..256", head_dim);
     FRB_CHECK_ARG(num_kv_heads >= 1 && num_heads % num_kv_heads == 0, "attention: %d heads are not a multiple of %d kv heads",
                   num_heads, num_kv_heads);
@@ -118,10 +126,10 @@ FRB_API int frb_attention_generic(const void* q, const void* k_pages, const void
     AttnParams p;
     p.q = q; p.k_pages = k_pages; p.v_pages = v_pages; p.page_table = page_table; p.tok_pos = tok_pos;
     p.tok_slot = tok_slot; p.out = out; p.scale = scale; p.window = window; p.max_pages = max_pages;
-    p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim;
+    p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim; p.v_dim = v_dim; p.slopes = slopes;
     const int group = num_heads / num_kv_heads;
     const int nwarps = group < 8 ? group : 8;
-    const size_t smem = ((size_t)KEY_BLOCK * (head_dim + 1) + (size_t)KEY_BLOCK * head_dim + (size_t)nwarps * head_dim) * sizeof(float);
+    const size_t smem = ((size_t)KEY_BLOCK * (head_dim + 1) + (size_t)KEY_BLOCK * v_dim + (size_t)nwarps * head_dim) * sizeof(float);
     dim3 grid(num_tokens, num_kv_heads);
     FRB_DISPATCH_DTYPE(dtype, T, {
         auto kernel = attention_generic_kernel<T>;

@@ -25,25 +25,31 @@ FRB_API int frb_abi_version() { return 3; }
 
 // ----------------------------------------------------------------------------- embedding rows
 
-template <typename WT>
+template <typename WT, typename AT>
 __global__ void embed_rows_kernel(const int* __restrict__ tokens, const WT* __restrict__ table, float* __restrict__ out,
-                                  int width, int vocab) {
+                                  AT* __restrict__ act, int width, int vocab, float scale) {
     after_previous_kernel();
     const int t = blockIdx.x;
     int token = tokens[t];
     if (token < 0 || token >= vocab) token = 0;      // ids are checked on the host before any launch
     const WT* row = table + (size_t)token * width;
     float* dst = out + (size_t)t * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) dst[i] = to_f32<WT>(row[i]);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = to_f32<WT>(row[i]) * scale;
+        dst[i] = v;
+        if (act) act[(size_t)t * width + i] = from_f32<AT>(v);
+    }
 }
 
-// out[t, :] = table[tokens[t], :] widened to float32 (no multiplier, src/minimax.rs:132).
+// out[t, :] = table[tokens[t], :] * scale in float32 (the reference has no multiplier, src/minimax.rs:132: scale 1);
+// `act`, if given, gets the same rows in its own type, for a layer whose sublayers read the stream itself.
 FRB_API int frb_embed_rows(const int* tokens, const void* table, int table_dtype, float* out, int num_tokens,
-                           int width, int vocab, cudaStream_t stream) {
+                           int width, int vocab, float scale, void* act, int act_dtype, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
-    FRB_DISPATCH_DTYPE(table_dtype, WT, {
-        launch_dependent(embed_rows_kernel<WT>, dim3(num_tokens), dim3(256), 0, stream, tokens, (const WT*)table, out, width, vocab);
-    });
+    FRB_DISPATCH_DTYPE(table_dtype, WT, FRB_DISPATCH_DTYPE(act_dtype, AT, {
+        launch_dependent(embed_rows_kernel<WT, AT>, dim3(num_tokens), dim3(256), 0, stream, tokens, (const WT*)table, out,
+                         (AT*)act, width, vocab, scale);
+    }));
     FRB_RETURN_LAUNCH("embed_rows");
 }
 
@@ -226,7 +232,8 @@ FRB_API int frb_rmsnorm(float* x, const float* delta, const float* expert_y, con
 // ----------------------------------------------------------------------------- Q/K norm + rotary + cache write
 
 struct QkvParams {
-    const void* qkv;          // [T, (nh + 2 nkv) * hd], InT
+    const void* qkv;          // [T, (nh + nkv) * hd + nkv * vd], InT
+    const float* bias;        // [(nh + nkv) * hd + nkv * vd] added to the row before anything else, or null
     const void* q_weight;     // [nh*hd] or null: no norm
     const void* k_weight;     // [nkv*hd] or null
     const float* cos_table;   // [positions, rotary_dim/2]
@@ -243,7 +250,16 @@ struct QkvParams {
     int per_head;             // the norm weights are [head_dim] and every head has a statistic of its own
     int tables_final;         // positions, slots and page table were complete before the kernel before this one began
     unsigned head_dim_inverse;   // ceil(2^32 / head_dim): the high word of n times this is n / head_dim for n < 2^24
+    int v_dim;                // size of a value head (the keys' head_dim unless the design says otherwise)
+    unsigned v_dim_inverse;
+    float q_temp_coef;        // the query is multiplied by 1 + coef * ln(floor((pos + 1) / every) + 1); 0: no such factor
+    int q_temp_every;
 };
+
+// The factor on a query at position `pos`, float32 throughout.
+__device__ __forceinline__ float query_temperature(float coef, int every, int pos) {
+    return coef == 0.f ? 1.f : 1.f + coef * logf((float)((pos + 1) / every) + 1.f);
+}
 
 #define QKV_BATCH 8          // elements a thread loads before it uses any of them
 
@@ -258,7 +274,8 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
     const int t = blockIdx.x;
     const int hd = p.head_dim;
     const int q_width = p.num_heads * hd, k_width = p.num_kv_heads * hd;
-    const int qk_width = q_width + k_width, all_width = qk_width + k_width;
+    const int vd = p.v_dim, v_width = p.num_kv_heads * vd;
+    const int qk_width = q_width + k_width, all_width = qk_width + v_width;
     const int half = p.rotary_dim / 2;
     float* s_cos = raw + all_width;
     float* s_sin = s_cos + half;
@@ -276,7 +293,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
 #pragma unroll
         for (int u = 0; u < QKV_BATCH; ++u) {
             const int i = base + u * NORM_BLOCK + threadIdx.x;
-            v[u] = i < all_width ? to_f32<InT>(src[i]) : 0.f;
+            v[u] = i < all_width ? to_f32<InT>(src[i]) + (p.bias ? p.bias[i] : 0.f) : 0.f;
             w[u] = 1.f;
             if (i < q_width) { if (qw) w[u] = to_f32<WT>(qw[p.per_head ? i % hd : i]); }
             else if (i < qk_width) { if (kw) w[u] = to_f32<WT>(kw[p.per_head ? (i - q_width) % hd : i - q_width]); }
@@ -300,6 +317,8 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
     float rinv_q = 1.f, rinv_k = 1.f;
     if (qw && !p.per_head) rinv_q = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssq, scratch) / (float)q_width + p.eps);
     if (kw && !p.per_head) rinv_k = 1.0f / sqrtf(block_sum<NORM_BLOCK>(ssk, scratch) / (float)k_width + p.eps);
+    const float q_temp = query_temperature(p.q_temp_coef, p.q_temp_every, pos);
+    rinv_q *= q_temp;
     __syncthreads();
     if (p.per_head) {
         // one statistic per head (q heads, then k heads): a warp sums a head's squares in a fixed order
@@ -318,7 +337,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
         const float* base = is_q ? raw : raw + q_width;
         const int local = is_q ? i : i - q_width;
         const int head = local / hd, dim = local - head * hd;
-        const float rinv = p.per_head ? s_rinv[(is_q ? 0 : p.num_heads) + head] : (is_q ? rinv_q : rinv_k);
+        const float rinv = p.per_head ? s_rinv[(is_q ? 0 : p.num_heads) + head] * (is_q ? q_temp : 1.f) : (is_q ? rinv_q : rinv_k);
         float value = base[local] * rinv;
         if (dim < p.rotary_dim) {
             int j, partner;
@@ -339,9 +358,9 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_kernel(QkvParams p) {
     }
     if (page >= 0) {
         const float* vrow = raw + qk_width;
-        for (int i = threadIdx.x; i < k_width; i += NORM_BLOCK) {
-            const int head = i / hd, dim = i - head * hd;
-            const size_t at = (((size_t)page * p.num_kv_heads + head) * hd + dim) * FRB_PAGE + in_page;
+        for (int i = threadIdx.x; i < v_width; i += NORM_BLOCK) {
+            const int head = i / vd, dim = i - head * vd;
+            const size_t at = (((size_t)page * p.num_kv_heads + head) * vd + dim) * FRB_PAGE + in_page;
             ((OutT*)p.v_pages)[at] = from_f32<OutT>(vrow[i]);
         }
     }
@@ -359,7 +378,8 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
     __shared__ float scratch[64];
     const int hd = p.head_dim;
     const int q_width = p.num_heads * hd, k_width = p.num_kv_heads * hd;
-    const int qk_width = q_width + k_width, all_width = qk_width + k_width;
+    const int vd = p.v_dim, v_width = p.num_kv_heads * vd;
+    const int qk_width = q_width + k_width, all_width = qk_width + v_width;
     int pos_early = 0, slot_early = 0, page_early = -1;
     // the blocks that transpose values come first in the grid: they run longest, and at the grid's end they ran alone
     const int token_block = (int)blockIdx.x - p.v_tiles;
@@ -381,7 +401,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
         // The values of 64 tokens of one kv head: read along the dimensions, written along the tokens, whose
         // places in a transposed page are neighbours whenever their positions are (a prompt's are).
         __shared__ int s_page[QKV_V_TOKENS], s_place[QKV_V_TOKENS];
-        OutT* tile = reinterpret_cast<OutT*>(raw);                       // [hd][QKV_V_TOKENS + 2]
+        OutT* tile = reinterpret_cast<OutT*>(raw);                       // [vd][QKV_V_TOKENS + 2]
         const int index = blockIdx.x;
         const int h = index % p.num_kv_heads, t0 = (index / p.num_kv_heads) * QKV_V_TOKENS;
         const int count = min(QKV_V_TOKENS, p.num_tokens - t0);
@@ -393,13 +413,15 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
         // a warp reads a token's dimensions, then writes a dimension's tokens: no division per element
         const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
         for (int j = warp; j < count; j += NORM_BLOCK / 32) {
-            const InT* row = (const InT*)p.qkv + (size_t)(t0 + j) * all_width + qk_width + h * hd;
-            for (int d = lane; d < hd; d += 32) tile[d * (QKV_V_TOKENS + 2) + j] = from_f32<OutT>(to_f32<InT>(row[d]));
+            const InT* row = (const InT*)p.qkv + (size_t)(t0 + j) * all_width + qk_width + h * vd;
+            const float* brow = p.bias ? p.bias + qk_width + h * vd : nullptr;
+            for (int d = lane; d < vd; d += 32)
+                tile[d * (QKV_V_TOKENS + 2) + j] = from_f32<OutT>(to_f32<InT>(row[d]) + (brow ? brow[d] : 0.f));
         }
         __syncthreads();
-        for (int d = warp; d < hd; d += NORM_BLOCK / 32) {
+        for (int d = warp; d < vd; d += NORM_BLOCK / 32) {
             for (int j = lane; j < count; j += 32) {
-                const size_t at = (((size_t)s_page[j] * p.num_kv_heads + h) * hd + d) * FRB_PAGE + s_place[j];
+                const size_t at = (((size_t)s_page[j] * p.num_kv_heads + h) * vd + d) * FRB_PAGE + s_place[j];
                 ((OutT*)p.v_pages)[at] = tile[d * (QKV_V_TOKENS + 2) + j];
             }
         }
@@ -423,6 +445,10 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
         for (int u = 0; u < QKV_VEC_BATCH; ++u) {
             const int i = base + 4 * (u * NORM_BLOCK + threadIdx.x);
             v[u] = i < row_width ? load4<InT>(src + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (p.bias && i < row_width) {
+                const float4 b = *reinterpret_cast<const float4*>(p.bias + i);
+                v[u] = make_float4(v[u].x + b.x, v[u].y + b.y, v[u].z + b.z, v[u].w + b.w);
+            }
             w[u] = make_float4(1.f, 1.f, 1.f, 1.f);
             if (i < q_width) { if (qw) w[u] = load4<WT>(qw + i); }
             else if (i < qk_width) { if (kw) w[u] = load4<WT>(kw + i - q_width); }
@@ -453,6 +479,7 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
     } else {
         __syncthreads();
     }
+    rinv_q *= query_temperature(p.q_temp_coef, p.q_temp_every, pos);
 
     for (int i = 4 * threadIdx.x; i < qk_width; i += 4 * NORM_BLOCK) {
         const bool is_q = i < q_width;
@@ -487,9 +514,9 @@ __global__ void __launch_bounds__(NORM_BLOCK) qkv_prepare_vec_kernel(QkvParams p
     }
     if (page >= 0 && !p.v_tiles) {
         const float* vrow = raw + qk_width;
-        for (int i = threadIdx.x; i < k_width; i += NORM_BLOCK) {
-            const int head = (int)__umulhi((unsigned)i, p.head_dim_inverse), dim = i - head * hd;
-            const size_t at = (((size_t)page * p.num_kv_heads + head) * hd + dim) * FRB_PAGE + in_page;
+        for (int i = threadIdx.x; i < v_width; i += NORM_BLOCK) {
+            const int head = (int)__umulhi((unsigned)i, p.v_dim_inverse), dim = i - head * vd;
+            const size_t at = (((size_t)page * p.num_kv_heads + head) * vd + dim) * FRB_PAGE + in_page;
             ((OutT*)p.v_pages)[at] = from_f32<OutT>(vrow[i]);
         }
     }
@@ -500,8 +527,11 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
                             const int* tok_pos, const int* tok_slot, const int* page_table, int max_pages,
                             void* q_out, void* k_pages, void* v_pages, int out_dtype, int num_tokens, int num_heads,
                             int num_kv_heads, int head_dim, int rotary_dim, int interleaved, int write_cache,
-                            int per_head, int tables_final, cudaStream_t stream) {
+                            int per_head, int tables_final, const float* bias, int v_dim, float q_temp_coef,
+                            int q_temp_every, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
+    if (v_dim <= 0) v_dim = head_dim;
+    FRB_CHECK_ARG(q_temp_coef == 0.f || q_temp_every >= 1, "qkv_prepare: a query temperature every %d positions", q_temp_every);
     FRB_CHECK_ARG(rotary_dim % 2 == 0 && rotary_dim <= head_dim, "qkv_prepare: rotary_dim %d must be even and <= head_dim %d",
                   rotary_dim, head_dim);
     FRB_CHECK_ARG(rotary_dim == 0 || (cos_table && sin_table && table_positions > 0), "qkv_prepare: rotary tables are missing");
@@ -514,15 +544,19 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
     p.num_tokens = num_tokens; p.v_tiles = 0; p.per_head = per_head && (q_weight || k_weight);
     p.tables_final = tables_final;
     p.head_dim_inverse = (unsigned)((0x100000000ull + (unsigned)head_dim - 1) / (unsigned)head_dim);
-    FRB_CHECK_ARG((long long)(num_heads + 2 * num_kv_heads) * head_dim < (1 << 24), "qkv_prepare: %d heads of %d", num_heads, head_dim);
+    p.bias = bias; p.v_dim = v_dim; p.q_temp_coef = q_temp_coef; p.q_temp_every = q_temp_every > 0 ? q_temp_every : 1;
+    p.v_dim_inverse = (unsigned)((0x100000000ull + (unsigned)v_dim - 1) / (unsigned)v_dim);
+    const long long all_width = (long long)(num_heads + num_kv_heads) * head_dim + (long long)num_kv_heads * v_dim;
+    FRB_CHECK_ARG(all_width < (1 << 24), "qkv_prepare: %d heads of %d", num_heads, head_dim);
     // per-head statistics: the squares of the q and k rows and one factor per head beside the rows
-    const size_t smem = ((size_t)(num_heads + 2 * num_kv_heads) * head_dim + rotary_dim +
+    const size_t smem = ((size_t)all_width + rotary_dim +
                          (p.per_head ? (size_t)(num_heads + num_kv_heads) * (head_dim + 1) : 0)) * sizeof(float);
     FRB_CHECK_ARG(smem <= 200 * 1024, "qkv_prepare: (heads + 2 kv heads) * head_dim = %d needs more than 200 KB of shared memory",
                   (num_heads + 2 * num_kv_heads) * head_dim);
     const int in_bytes = in_dtype == FRB_F32 ? 4 : 2, out_bytes = out_dtype == FRB_F32 ? 4 : 2, w_bytes = weight_dtype == FRB_F32 ? 4 : 2;
     const auto aligned = [](const void* ptr, int bytes) { return ((uintptr_t)ptr & (size_t)(4 * bytes - 1)) == 0; };
-    const bool by_four = !p.per_head && head_dim % 4 == 0 && rotary_dim % (interleaved ? 4 : 8) == 0 && aligned(qkv, in_bytes) &&
+    const bool by_four = !p.per_head && head_dim % 4 == 0 && v_dim % 4 == 0 && aligned(bias, 4) &&
+                         rotary_dim % (interleaved ? 4 : 8) == 0 && aligned(qkv, in_bytes) &&
                          aligned(q_out, out_bytes) && aligned(k_pages, out_bytes) && aligned(q_weight, w_bytes) &&
                          aligned(k_weight, w_bytes);
     FRB_DISPATCH_DTYPE(in_dtype, InT, FRB_DISPATCH_DTYPE(out_dtype, OutT, FRB_DISPATCH_DTYPE(weight_dtype, WT, {
@@ -534,7 +568,7 @@ FRB_API int frb_qkv_prepare(const void* qkv, int in_dtype, const void* q_weight,
             // many tokens: the values go through blocks of their own (64 tokens of a kv head), which write them
             // along the tokens instead of one two-byte store per token and dimension
 
-            const size_t tile_bytes = (size_t)head_dim * (QKV_V_TOKENS + 2) * sizeof(OutT);
+            const size_t tile_bytes = (size_t)v_dim * (QKV_V_TOKENS + 2) * sizeof(OutT);
             const size_t bytes = smem > tile_bytes ? smem : tile_bytes;
             auto kernel = qkv_prepare_vec_kernel<InT, OutT, WT, 256>;
             if (bytes > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
@@ -582,4 +616,42 @@ FRB_API int frb_gated_unit(const float* both, void* out, int out_dtype, int rows
         gated_unit_kernel<OutT><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(both, (OutT*)out, width, total);
     });
     FRB_RETURN_LAUNCH("gated_unit");
+}
+
+// out[t, i] = act(in[t, i]) in OutT, for a feed-forward of one product in and one out.
+// kind 0: relu(z)^2; 1: gelu_tanh(z) = 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))); 2: silu; 3: relu.
+template <typename OutT>
+__global__ void unary_unit_kernel(const float* __restrict__ in, OutT* __restrict__ out, int kind, size_t total) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    const float z = in[i];
+    float r;
+    if (kind == 0) { const float m = fmaxf(z, 0.f); r = m * m; }
+    else if (kind == 1) r = 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    else if (kind == 2) r = z / (1.0f + expf(-z));
+    else r = fmaxf(z, 0.f);
+    out[i] = from_f32<OutT>(r);
+}
+
+FRB_API int frb_unary_unit(const float* in, void* out, int out_dtype, long long total, int kind, cudaStream_t stream) {
+    if (total == 0) return 0;
+    FRB_CHECK_ARG(kind >= 0 && kind <= 3, "unary_unit: activation %d is none of 0..3", kind);
+    FRB_DISPATCH_DTYPE(out_dtype, OutT, {
+        unary_unit_kernel<OutT><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(in, (OutT*)out, kind, (size_t)total);
+    });
+    FRB_RETURN_LAUNCH("unary_unit");
+}
+
+// x[i] = cap * tanh(x[i] / cap), in place on float32 logits.
+__global__ void softcap_kernel(float* __restrict__ x, float cap, size_t total) {
+    after_previous_kernel();
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < total) x[i] = cap * tanhf(x[i] / cap);
+}
+
+FRB_API int frb_softcap(float* x, long long total, float cap, cudaStream_t stream) {
+    if (total == 0) return 0;
+    FRB_CHECK_ARG(cap > 0.f, "softcap: a cap of %f", (double)cap);
+    launch_dependent(softcap_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, stream, x, cap, (size_t)total);
+    FRB_RETURN_LAUNCH("softcap");
 }

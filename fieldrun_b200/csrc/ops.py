@@ -20,12 +20,16 @@ _P, _I, _F, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlon
 
 # entry point -> argument types ('p' pointer, 'i' int, 'f' float, 'l' long long); the stream is appended
 _SIGNATURES = {
-    "frb_embed_rows": "ppipiii",
+    "frb_embed_rows": "ppipiiifpi",
     "frb_rmsnorm": "pppppippifiipipi",
-    "frb_qkv_prepare": "pippifppipppipppiiiiiiiiii",
+    "frb_qkv_prepare": "pippifppipppipppiiiiiiiiiipifi",
     "frb_wait_probe": "lpp",
     "frb_add_rows": "ppl",
-    "frb_attention_generic": "pppipipppiiiifi",
+    "frb_attention_generic": "pppipipppiiiifiip",
+    "frb_layernorm": "ppppfppiii",
+    "frb_unary_unit": "ppili",
+    "frb_softcap": "plf",
+    "frb_gla_scan": "piiiiiipipppppppiiiiiifff",
     "frb_router_topk": "ppiiiifpp",
     "frb_expert_plan": "piiiippppppp",
     "frb_expert_combine": "pppiiip",
@@ -191,12 +195,69 @@ def _want(t: torch.Tensor, dtype: torch.dtype, what: str) -> None:
 
 # ------------------------------------------------------------------------------------------------
 
-def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor) -> None:
-    """out[t] = table[tokens[t]] as float32."""
+def embed_rows(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, scale: float = 1.0,
+               act: Optional[torch.Tensor] = None) -> None:
+    """out[t] = table[tokens[t]] * scale as float32; ``act`` gets the same rows in its own dtype."""
     _want(tokens, torch.int32, "tokens")
     _want(out, torch.float32, "the residual stream")
     vocab, width = table.shape
-    _call("frb_embed_rows", _ptr(tokens), _ptr(table), _code(table.dtype), _ptr(out), tokens.numel(), width, vocab)
+    _call("frb_embed_rows", _ptr(tokens), _ptr(table), _code(table.dtype), _ptr(out), tokens.numel(), width, vocab,
+          float(scale), _ptr(act), _code(act.dtype) if act is not None else 0)
+
+
+def layernorm(rows_in: torch.Tensor, weight: torch.Tensor, bias: Optional[torch.Tensor], eps: float, *,
+              rows: Optional[torch.Tensor] = None, stream: Optional[torch.Tensor] = None,
+              act: Optional[torch.Tensor] = None) -> None:
+    """y = layer norm of ``rows_in[rows[r]]`` (or row r) with weight and bias, float32 statistics.  With ``stream``
+    (float32, the rows in order) y is added to it in place and ``act`` gets the new stream in its own dtype; without,
+    ``act`` gets y."""
+    _want(rows_in, torch.float32, "rows to norm")
+    _want(weight, torch.float32, "norm weight")
+    if bias is not None:
+        _want(bias, torch.float32, "norm bias")
+    if stream is not None:
+        _want(stream, torch.float32, "the residual stream")
+    if rows is not None:
+        _want(rows, torch.int32, "row indices")
+    if stream is None and act is None:
+        raise KernelError("a layer norm with nowhere to put its result")
+    count = rows.numel() if rows is not None else rows_in.shape[0]
+    _call("frb_layernorm", _ptr(rows_in), _ptr(rows), _ptr(weight), _ptr(bias), float(eps), _ptr(stream), _ptr(act),
+          _code(act.dtype) if act is not None else 0, count, rows_in.shape[-1])
+
+
+ACTIVATIONS = {"relu_squared": 0, "gelu_tanh": 1, "silu": 2, "relu": 3}
+
+
+def unary_unit(rows_in: torch.Tensor, out: torch.Tensor, activation: str) -> None:
+    """out = activation(rows_in) in out's dtype; ``activation`` is a key of ``ACTIVATIONS``."""
+    _want(rows_in, torch.float32, "rows before the activation")
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"activation {activation!r} is none of {sorted(ACTIVATIONS)}")
+    _call("frb_unary_unit", _ptr(rows_in), _ptr(out), _code(out.dtype), rows_in.numel(), ACTIVATIONS[activation])
+
+
+def softcap(logits: torch.Tensor, cap: float) -> None:
+    """logits <- cap * tanh(logits / cap), in place."""
+    _want(logits, torch.float32, "logits")
+    _call("frb_softcap", _ptr(logits), logits.numel(), float(cap))
+
+
+def gla_scan(proj: torch.Tensor, offsets: tuple[int, int, int, int, int], a2: torch.Tensor, a2_bias: torch.Tensor,
+             norm_weight: torch.Tensor, state: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor,
+             cu_q_len: torch.Tensor, out: torch.Tensor, *, heads: int, dim: int, vdim: int, tau: float, q_scale: float,
+             eps: float) -> None:
+    """Gated linear attention over the step's new tokens (see gla.cu): ``proj`` float32 [T, P] holds q, k, v, g and
+    the decay's inner rows at ``offsets``; ``state`` float32 [slots, 2, heads, dim, vdim]; ``out`` [T, heads * vdim]."""
+    _want(proj, torch.float32, "projected rows")
+    _want(state, torch.float32, "the recurrent state")
+    _want(a2_bias, torch.float32, "the decay's bias")
+    _want(norm_weight, torch.float32, "the output norm's weight")
+    if tuple(state.shape[1:]) != (2, heads, dim, vdim):
+        raise KernelError(f"the recurrent state is {list(state.shape)}, not [slots, 2, {heads}, {dim}, {vdim}]")
+    _call("frb_gla_scan", _ptr(proj), proj.shape[1], *[int(o) for o in offsets], _ptr(a2), _code(a2.dtype), _ptr(a2_bias),
+          _ptr(norm_weight), _ptr(state), _ptr(seq_slot), _ptr(seq_start), _ptr(cu_q_len), _ptr(out), _code(out.dtype),
+          seq_slot.numel(), heads, dim, vdim, a2.shape[1], float(tau), float(q_scale), float(eps))
 
 
 NORM_MAX_SUMMED_ROWS = 32      # most weighted rows per token that the norm kernel sums itself (NORM_MAX_TOP_K)
@@ -241,14 +302,22 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
                 tok_slot: torch.Tensor, page_table: Optional[torch.Tensor], q_out: torch.Tensor,
                 k_pages: Optional[torch.Tensor], v_pages: Optional[torch.Tensor], *, num_heads: int,
                 num_kv_heads: int, head_dim: int, rotary_dim: int, interleaved: bool, write_cache: bool,
-                per_head: bool = False, tables_final: bool = False) -> None:
+                per_head: bool = False, tables_final: bool = False, bias: Optional[torch.Tensor] = None,
+                v_dim: Optional[int] = None, q_temp: Optional[tuple[float, int]] = None) -> None:
     """Q/K RMSNorm (when weights are given: over the whole row with weights [heads * head_dim], or with
     ``per_head`` over each head with weights [head_dim]), rotary from the tables, Q out, K/V into their pages.
     ``tables_final``: positions, slots and the page table were complete before the kernel before this one in
     the stream began (a step's tables, with the projection between them and this call); the kernel then reads
-    them, and the angles, while that kernel still runs."""
-    if (q_weight is None) != (k_weight is None):
+    them, and the angles, while that kernel still runs.  ``bias`` (float32, as wide as a row of ``qkv``) is added
+    first; ``v_dim`` is the size of a value head if it is not ``head_dim``; ``q_temp`` = (coef, every) multiplies the
+    query at position p by 1 + coef * ln(floor((p + 1) / every) + 1).  A row without keys and values (a layer that
+    reads another layer's cache line) is ``num_kv_heads = 0`` with ``write_cache`` false."""
+    if (q_weight is None) != (k_weight is None) and num_kv_heads > 0:
         raise KernelError("q and k norm weights come together or not at all")
+    if bias is not None:
+        _want(bias, torch.float32, "the projections' bias")
+    if num_kv_heads == 0 and write_cache:
+        raise KernelError("a row without keys and values cannot write the cache")
     wdtype = q_weight.dtype if q_weight is not None else torch.float32
     if k_weight is not None and k_weight.dtype != wdtype:
         raise KernelError("q and k norm weights must have one dtype")
@@ -262,17 +331,23 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
     _call("frb_qkv_prepare", _ptr(qkv), _code(qkv.dtype), _ptr(q_weight), _ptr(k_weight), _code(wdtype), float(eps),
           _ptr(cos_table), _ptr(sin_table), table_positions, _ptr(tok_pos), _ptr(tok_slot), _ptr(page_table), max_pages,
           _ptr(q_out), _ptr(k_pages), _ptr(v_pages), _code(out_dtype), qkv.shape[0], num_heads, num_kv_heads, head_dim,
-          rotary_dim, int(interleaved), int(write_cache), int(per_head), int(tables_final))
+          rotary_dim, int(interleaved), int(write_cache), int(per_head), int(tables_final), _ptr(bias),
+          int(v_dim or head_dim), float(q_temp[0]) if q_temp else 0.0, int(q_temp[1]) if q_temp else 1)
 
 
 def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
                       tok_pos: torch.Tensor, tok_slot: torch.Tensor, out: torch.Tensor, *, num_heads: int,
-                      num_kv_heads: int, head_dim: int, scale: float, window: Optional[int]) -> None:
+                      num_kv_heads: int, head_dim: int, scale: float, window: Optional[int], v_dim: Optional[int] = None,
+                      slopes: Optional[torch.Tensor] = None) -> None:
+    """``v_dim``: size of a value head if not ``head_dim``; ``slopes`` (float32 [num_heads]): the score of key j for
+    the query at position i is lowered by slopes[h] * (i - j)."""
     if k_pages.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("queries, cache and output must have one dtype")
+    if slopes is not None:
+        _want(slopes, torch.float32, "distance slopes")
     _call("frb_attention_generic", _ptr(q), _ptr(k_pages), _ptr(v_pages), _code(q.dtype), _ptr(page_table),
           page_table.shape[1], _ptr(tok_pos), _ptr(tok_slot), _ptr(out), q.shape[0], num_heads, num_kv_heads, head_dim,
-          float(scale), int(window or 0))
+          float(scale), int(window or 0), int(v_dim or head_dim), _ptr(slopes))
 
 
 def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, renormalize: bool, routed_scale: float,

@@ -45,9 +45,9 @@ class DecoderModel:
             self.blocks.append(build_block(
                 layer.block,
                 build_part("mixer", layer.mixer, self.dtype),
-                build_part("feed_forward", layer.feed_forward, self.dtype),
+                build_part("feed_forward", layer.feed_forward, self.dtype) if layer.feed_forward is not None else None,
                 build_part("norm", layer.mixer_norm, self.dtype),
-                build_part("norm", layer.feed_forward_norm, self.dtype)))
+                build_part("norm", layer.feed_forward_norm, self.dtype) if layer.feed_forward_norm is not None else None))
         self.final_norm = build_part("norm", plan.final_norm, self.dtype)
         self.head = build_part("head", plan.head, self.dtype)
         self.head_is_tied = plan.head.tensors.get("weight") == plan.embedding.tensors.get("weight")

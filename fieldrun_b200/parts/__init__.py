@@ -1,5 +1,5 @@
 """Parts that layers are put together from.  Importing the package registers the built-in kinds."""
-from . import attention, block, embedding, feed_forward, norm, position  # noqa: F401
+from . import attention, block, embedding, feed_forward, linear_attention, norm, position  # noqa: F401
 from .base import (Block, DeferredUpdate, WeightedRows, FeedForward, Mixer, Norm, Part, Position, as_tensor, build_block, build_part,
                    build_position, register_part, registered)
 

@@ -9,6 +9,14 @@ the token's absolute position; K (normed, rotated) and V written to the cache
 line; every query head h attends, with keys of head h // (heads / kv_heads), over
 the keys it may see; output projection without bias (src/minimax.rs:253-282).
 The three projections are held as one matrix so that one product makes q|k|v.
+
+Optional constants beyond the reference's model, each an argument: ``value_dim`` (a value head of another
+size than a key head), ``bias`` (q, k and v projections with biases, added in float32 to the product's
+result), ``query_temperature`` ``{"coef", "every"}`` (the normed query at position p is multiplied by
+1 + coef * ln(floor((p + 1) / every) + 1)), ``distance_slopes`` (one slope per query head: the score of key j
+for the query at position i is lowered by slope * (i - j); this is the position encoding that is not a rotation),
+``shares_kv`` (the layer has no key and value projections: it attends, with its own queries, over the cache
+line of an earlier layer, which the plan's run order names).
 """
 from __future__ import annotations
 
@@ -36,6 +44,18 @@ class GQAAttention(Mixer):
         self.num_heads = int(a["num_heads"])
         self.num_kv_heads = int(a["num_kv_heads"])
         self.head_dim = int(a["head_dim"])
+        self.value_dim = int(a.get("value_dim") or self.head_dim)
+        self.has_bias = bool(a.get("bias", False))
+        self.shares_kv = bool(a.get("shares_kv", False))
+        temperature = a.get("query_temperature")
+        self.q_temp = (float(temperature["coef"]), int(temperature["every"])) if temperature else None
+        if self.q_temp is not None and self.q_temp[1] < 1:
+            raise ValueError(f"a query temperature every {self.q_temp[1]} positions")
+        slopes = a.get("distance_slopes")
+        self.slope_values = tuple(float(s) for s in slopes) if slopes is not None else None
+        if self.slope_values is not None and len(self.slope_values) != self.num_heads:
+            raise ValueError(f"{len(self.slope_values)} distance slopes for {self.num_heads} heads")
+        self.slopes: Optional[torch.Tensor] = None
         self.qk_norm = a.get("qk_norm", "none")
         if self.qk_norm not in ("none", "full_width", "per_head"):
             raise ValueError(f"qk_norm {self.qk_norm!r} is none of 'none', 'full_width', 'per_head'")
@@ -48,11 +68,16 @@ class GQAAttention(Mixer):
             raise ValueError(f"{self.num_heads} heads are not a multiple of {self.num_kv_heads} kv heads")
         if not 1 <= self.head_dim <= 256:
             raise ValueError(f"head_dim {self.head_dim} is outside the kernels' range 1..256")
+        if not 1 <= self.value_dim <= 256:
+            raise ValueError(f"value_dim {self.value_dim} is outside the kernels' range 1..256")
         self.position = build_position(a.get("position"))
         if self.position is not None and self.position.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim {self.position.rotary_dim} exceeds head_dim {self.head_dim}")
         self.q_width = self.num_heads * self.head_dim
         self.kv_width = self.num_kv_heads * self.head_dim
+        self.v_width = self.num_kv_heads * self.value_dim
+        self.out_width = self.num_heads * self.value_dim
+        self.b_qkv: Optional[torch.Tensor] = None
         self.w_qkv: Optional[torch.Tensor] = None
         self.w_o: Optional[torch.Tensor] = None
         self.q_norm: Optional[torch.Tensor] = None
@@ -65,15 +90,22 @@ class GQAAttention(Mixer):
         needs = {
             "q_proj": TensorNeed(self.name_of("q_proj"), (self.q_width, self.hidden_size), MATRIX, "normal"),
             "k_proj": TensorNeed(self.name_of("k_proj"), (self.kv_width, self.hidden_size), MATRIX, "normal"),
-            "v_proj": TensorNeed(self.name_of("v_proj"), (self.kv_width, self.hidden_size), MATRIX, "normal"),
-            "o_proj": TensorNeed(self.name_of("o_proj"), (self.hidden_size, self.q_width), MATRIX, "normal"),
+            "v_proj": TensorNeed(self.name_of("v_proj"), (self.v_width, self.hidden_size), MATRIX, "normal"),
+            "o_proj": TensorNeed(self.name_of("o_proj"), (self.hidden_size, self.out_width), MATRIX, "normal"),
         }
+        if self.has_bias:
+            needs["q_bias"] = TensorNeed(self.name_of("q_bias"), (self.q_width,), VECTOR, "bias")
+            needs["k_bias"] = TensorNeed(self.name_of("k_bias"), (self.kv_width,), VECTOR, "bias")
+            needs["v_bias"] = TensorNeed(self.name_of("v_bias"), (self.v_width,), VECTOR, "bias")
         if self.qk_norm == "full_width":
             needs["q_norm"] = TensorNeed(self.name_of("q_norm"), (self.q_width,), VECTOR, "around_one")
             needs["k_norm"] = TensorNeed(self.name_of("k_norm"), (self.kv_width,), VECTOR, "around_one")
         elif self.qk_norm == "per_head":
             needs["q_norm"] = TensorNeed(self.name_of("q_norm"), (self.head_dim,), VECTOR, "around_one")
             needs["k_norm"] = TensorNeed(self.name_of("k_norm"), (self.head_dim,), VECTOR, "around_one")
+        if self.shares_kv:                       # keys and values, with all that makes them, are another layer's
+            for local in ("k_proj", "v_proj", "k_bias", "v_bias", "k_norm"):
+                needs.pop(local, None)
         return needs
 
     def tensor_needs(self):
@@ -81,34 +113,45 @@ class GQAAttention(Mixer):
 
     def load(self, source: TensorSource) -> None:
         needs = self._needs()
-        self.w_qkv = torch.cat([source.fetch(needs[n]) for n in ("q_proj", "k_proj", "v_proj")], dim=0).contiguous()
+        projections = ("q_proj",) if self.shares_kv else ("q_proj", "k_proj", "v_proj")
+        self.w_qkv = torch.cat([source.fetch(needs[n]) for n in projections], dim=0).contiguous()
         self.w_o = source.fetch(needs["o_proj"])
+        if self.has_bias:
+            biases = ("q_bias",) if self.shares_kv else ("q_bias", "k_bias", "v_bias")
+            self.b_qkv = torch.cat([source.fetch(needs[n]) for n in biases], dim=0).contiguous()
         if self.qk_norm != "none":
             self.q_norm = source.fetch(needs["q_norm"])
-            self.k_norm = source.fetch(needs["k_norm"])
+            self.k_norm = source.fetch(needs["k_norm"]) if "k_norm" in needs else None
 
     # -- cache and tables ----------------------------------------------------------------------------
     def cache_need(self) -> CacheNeed:
         return CacheNeed(kv_heads=self.num_kv_heads, head_dim=self.head_dim,
-                         window=int(self.window) if self.window is not None else None)
+                         window=int(self.window) if self.window is not None else None,
+                         value_dim=self.value_dim if self.value_dim != self.head_dim else 0)
 
     def prepare(self, num_positions: int, device) -> None:
         if self.position is not None and self.position.rotary_dim > 0:
             self.cos, self.sin = self.position.shared_tables(num_positions, device)
+        if self.slope_values is not None:
+            self.slopes = torch.tensor(self.slope_values, dtype=torch.float64).to(torch.float32).to(device)
 
     # -- one step --------------------------------------------------------------------------------------
     def forward(self, ctx, act: torch.Tensor, line: LineView, writes_cache: bool) -> torch.Tensor:
         tokens = act.shape[0]
-        qkv = linear(act, self.w_qkv)                                        # float32 [T, q + 2 kv]
+        if self.shares_kv and writes_cache:
+            raise ValueError("an attention layer without keys and values of its own was asked to write a cache line")
+        qkv = linear(act, self.w_qkv)                                        # float32 [T, q + k + v] (or [T, q])
         q = ctx.buffer("attention.q", (tokens, self.q_width), self.dtype)
         rotary_dim = self.position.rotary_dim if self.position is not None else 0
         ops.qkv_prepare(qkv, self.q_norm, self.k_norm, self.qk_norm_eps, self.cos, self.sin, ctx.tok_pos, ctx.tok_slot,
                         line.page_table, q, line.keys, line.values, num_heads=self.num_heads,
-                        num_kv_heads=self.num_kv_heads, head_dim=self.head_dim, rotary_dim=rotary_dim,
+                        num_kv_heads=0 if self.shares_kv else self.num_kv_heads, head_dim=self.head_dim,
+                        rotary_dim=rotary_dim,
                         interleaved=bool(self.position.interleaved) if self.position is not None else False,
                         write_cache=writes_cache, per_head=self.qk_norm == "per_head",
-                        tables_final=True)      # the step's tables were there before the projection above began
-        out = ctx.buffer("attention.out", (tokens, self.q_width), self.dtype)
+                        tables_final=True,      # the step's tables were there before the projection above began
+                        bias=self.b_qkv, v_dim=self.value_dim, q_temp=self.q_temp)
+        out = ctx.buffer("attention.out", (tokens, self.out_width), self.dtype)
         self.attend(ctx, q, line, out)
         return linear(out, self.w_o)
 
@@ -117,7 +160,8 @@ class GQAAttention(Mixer):
         sizes 64 and 128, mma.sync otherwise); the general kernel for everything else."""
         common = dict(num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                       scale=self.softmax_scale, window=self.window)
-        if self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
+        plain = self.slopes is None and self.value_dim == self.head_dim
+        if plain and self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
             if ctx.is_decode and self.num_heads // self.num_kv_heads <= 16:
                 chunks = (ctx.max_kv_len + ops.ATTENTION_CHUNK - 1) // ops.ATTENTION_CHUNK
                 part_o = ctx.buffer("attention.part_o", (ctx.num_seqs, self.num_heads, chunks, self.head_dim), torch.float32)
@@ -138,7 +182,7 @@ class GQAAttention(Mixer):
             return
         ops.attention_generic(q, line.keys, line.values, line.page_table, ctx.tok_pos, ctx.tok_slot, out,
                               num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
-                              scale=self.softmax_scale, window=self.window)
+                              scale=self.softmax_scale, window=self.window, v_dim=self.value_dim, slopes=self.slopes)
 
 
 register_part("mixer", "gqa_attention", GQAAttention, replace=True)

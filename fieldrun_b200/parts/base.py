@@ -18,6 +18,8 @@ Interfaces
 ``Position.tables(num_positions, device)`` -> (cos, sin) float32 [positions, dim/2]
 ``Block.forward(ctx, x, pending, line, writes_cache)`` -> (x, pending)
     ``pending`` is an update not yet added to x, so that the next norm adds it.
+``Norm.add_normed(ctx, update, x)`` -> x in the model dtype
+    the other place of a norm: x <- x + norm(update), for blocks whose sublayers read x itself.
 """
 from __future__ import annotations
 
@@ -101,6 +103,11 @@ class Norm(Part):
                 rows: Optional[torch.Tensor] = None, want32: bool = False, write_back: bool = True):
         raise NotImplementedError
 
+    def add_normed(self, ctx, update: torch.Tensor, x: torch.Tensor) -> torch.Tensor:
+        """For a block whose norm sits on the sublayer's output: x <- x + norm(update) in float32, in place;
+        returns the new x in the model dtype (x itself in float32 mode), which the next sublayer reads."""
+        raise NotImplementedError(f"norm {self.spec.kind!r} has no form that norms a sublayer's output")
+
 
 class Position:
     """A position encoding handed to a mixer: it fills the tables the mixer's kernel rotates with.
@@ -151,7 +158,8 @@ class Block:
         self.mixer_norm, self.feed_forward_norm = mixer_norm, feed_forward_norm
 
     def parts(self) -> list[Part]:
-        return [self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward]
+        """The block's parts; a layer without a feed-forward has neither it nor its norm."""
+        return [part for part in (self.mixer_norm, self.mixer, self.feed_forward_norm, self.feed_forward) if part is not None]
 
     def forward(self, ctx, x, pending, line: LineView, writes_cache: bool):
         raise NotImplementedError

@@ -1,9 +1,13 @@
 """The arrangement of a layer: norm -> mixer -> residual, norm -> feed-forward -> residual
 (the reference's two-norm pre-norm block, src/minimax.rs:261-284).  Each residual sum is
-left to the norm that follows it, which adds in float32 while it reads the stream."""
+left to the norm that follows it, which adds in float32 while it reads the stream.
+A second arrangement, ``output_norm``, has the norm behind the sublayer instead of in front of it."""
 from __future__ import annotations
 
+import torch
+
 from .base import Block, as_tensor, register_part
+from .norm import LayerNorm
 
 
 class PreNormBlock(Block):
@@ -19,4 +23,35 @@ class PreNormBlock(Block):
         return x, self.feed_forward.forward_deferred(ctx, act2, act2_32)
 
 
+class OutputNormBlock(Block):
+    """The norm on the sublayer's output only: x <- x + norm1(mixer(x)), then, if the layer has a feed-forward,
+    x <- x + norm2(feed_forward(x)).  The sublayers read x itself, so besides the float32 stream its copy in the
+    model dtype goes from sublayer to sublayer: the norm that adds to the stream writes it (``Norm.add_normed``),
+    an embedding with ``typed_copy`` writes the first one."""
+
+    def stream_copy(self, ctx, x, pending):
+        if pending is not None:                            # a block before this one left its update to the next norm
+            from ..csrc import ops
+            ops.add_rows(x, as_tensor(ctx, pending))
+            ctx.stream_copy_rows = -1
+        if x.dtype == self.mixer.dtype:
+            return x
+        act = ctx.buffer(LayerNorm.STREAM_COPY, tuple(x.shape), self.mixer.dtype)
+        if getattr(ctx, "stream_copy_rows", -1) != x.shape[0]:
+            act.copy_(x)                                   # nobody wrote the copy of this step's stream yet
+        return act
+
+    def forward(self, ctx, x, pending, line, writes_cache):
+        act = self.stream_copy(ctx, x, pending)
+        update = as_tensor(ctx, self.mixer.forward(ctx, act, line, writes_cache))
+        act = self.mixer_norm.add_normed(ctx, update, x)
+        if self.feed_forward is not None:
+            act32 = x if self.feed_forward.wants_float32_input else None
+            update = as_tensor(ctx, self.feed_forward.forward_deferred(ctx, act, act32))
+            self.feed_forward_norm.add_normed(ctx, update, x)
+        ctx.stream_copy_rows = x.shape[0]
+        return x, None
+
+
 register_part("block", "pre_norm", PreNormBlock, replace=True)
+register_part("block", "output_norm", OutputNormBlock, replace=True)

@@ -268,5 +268,40 @@ class DenseGatedUnit(FeedForward):
         return linear(hidden, self.w_down)
 
 
+class DenseUnit(FeedForward):
+    """W_down act(W_up x): one product in, an activation, one product out.  ``activation`` is one of
+    ``ops.ACTIVATIONS`` (``relu_squared``: relu(z)^2, ``gelu_tanh``, ``silu``, ``relu``)."""
+
+    replayable = True
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        self.hidden_size = int(spec.args["hidden_size"])
+        self.width = int(spec.args["width"])
+        self.activation = str(spec.args["activation"])
+        if self.activation not in ops.ACTIVATIONS:
+            raise ValueError(f"activation {self.activation!r} is none of {sorted(ops.ACTIVATIONS)}")
+        self.w_up: Optional[torch.Tensor] = None
+        self.w_down: Optional[torch.Tensor] = None
+
+    def _needs(self):
+        d, i = self.hidden_size, self.width
+        return (TensorNeed(self.name_of("w_up"), (i, d), MATRIX, "normal"),
+                TensorNeed(self.name_of("w_down"), (d, i), MATRIX, "normal"))
+
+    def tensor_needs(self):
+        return list(self._needs())
+
+    def load(self, source: TensorSource) -> None:
+        self.w_up, self.w_down = (source.fetch(n) for n in self._needs())
+
+    def forward(self, ctx, act, act32):
+        up = linear(act, self.w_up)                                # float32 [T, I]
+        hidden = ctx.buffer("dense.hidden", (act.shape[0], self.width), self.dtype)
+        ops.unary_unit(up, hidden, self.activation)
+        return linear(hidden, self.w_down)
+
+
 register_part("feed_forward", "routed_experts", RoutedExperts, replace=True)
+register_part("feed_forward", "dense_unit", DenseUnit, replace=True)
 register_part("feed_forward", "dense_gated", DenseGatedUnit, replace=True)

@@ -46,4 +46,60 @@ class RMSNorm(Norm):
         return out, out32
 
 
+class LayerNorm(Norm):
+    """(v - mean) / sqrt(var + eps) * weight + bias per row, var the mean of the squared deviations, float32
+    statistics; the bias is optional (``bias: False``).  It serves in both places of a norm: on the stream
+    (``forward``: a model's last norm, or a pre-norm block) and on a sublayer's output (``add_normed``), where
+    one kernel norms the update, adds it to the float32 stream and writes the stream's copy in the model dtype."""
+
+    replayable = True
+    STREAM_COPY = "stream.act"           # the workspace buffer that holds the stream in the model dtype
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        self.width = int(spec.args["width"])
+        self.eps = float(spec.args["eps"])
+        self.has_bias = bool(spec.args.get("bias", True))
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+
+    def tensor_needs(self):
+        needs = [TensorNeed(self.name_of("weight"), (self.width,), VECTOR, "around_one")]
+        if self.has_bias:
+            needs.append(TensorNeed(self.name_of("bias"), (self.width,), VECTOR, "bias"))
+        return needs
+
+    def load(self, source: TensorSource) -> None:
+        needs = self.tensor_needs()
+        self.weight = source.fetch(needs[0])
+        self.bias = source.fetch(needs[1]) if self.has_bias else None
+
+    def forward(self, ctx, x, *, delta=None, rows=None, want32=False, write_back=True):
+        delta = as_tensor(ctx, delta)
+        if delta is not None:
+            if write_back:
+                ops.add_rows(x, delta)
+            else:
+                x = x + delta
+        count = rows.numel() if rows is not None else x.shape[0]
+        out = ctx.buffer(f"norm.out.{self.width}", (count, self.width), self.dtype)
+        ops.layernorm(x, self.weight, self.bias, self.eps, rows=rows, act=out)
+        out32 = None
+        if want32:
+            out32 = out
+            if self.dtype != torch.float32:
+                out32 = ctx.buffer(f"norm.out32.{self.width}", (count, self.width), torch.float32)
+                ops.layernorm(x, self.weight, self.bias, self.eps, rows=rows, act=out32)
+        return out, out32
+
+    def add_normed(self, ctx, update, x):
+        if self.dtype == torch.float32:
+            ops.layernorm(update, self.weight, self.bias, self.eps, stream=x)
+            return x
+        act = ctx.buffer(self.STREAM_COPY, tuple(x.shape), self.dtype)
+        ops.layernorm(update, self.weight, self.bias, self.eps, stream=x, act=act)
+        return act
+
+
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
+register_part("norm", "layernorm", LayerNorm, replace=True)
