@@ -66,7 +66,7 @@ def bamasun_plan(cfg: BamasunConfig) -> ModelPlan:
                 tensors=tensors,
             )
             if m.kv_from is None:
-                line_of[index] = len(line_of)
+                line_of[index] = max(line_of.values(), default=-1) + 1
                 runs.append(RunSpec(layer=index, cache_line=line_of[index], writes_cache=True))
             else:
                 line_of[index] = line_of[m.kv_from]
