@@ -134,6 +134,8 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
             q[step][0] = q0 ? __ldg(reinterpret_cast<const uint4*>(q0 + 32 * step) + t) : make_uint4(0, 0, 0, 0);
             q[step][1] = q1 ? __ldg(reinterpret_cast<const uint4*>(q1 + 32 * step) + t) : make_uint4(0, 0, 0, 0);
         }
+        float slope2[2];
+        group_slopes(p.slopes, kvh * group, group, g, slope2);
         for (int n = 0; DT_WARPS * n + warp < num_pages && ok; ++n) {
             const int key_base = (first_page + DT_WARPS * n + warp) * FRB_PAGE;
             const int k_stage = 2 * warp, v_stage = 2 * warp + 1;
@@ -158,8 +160,10 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
                             mma_bf16(acc, q[step][0].x, q[step][1].x, q[step][0].y, q[step][1].y, kb.x, kb.y);
                             mma_bf16(acc, q[step][0].z, q[step][1].z, q[step][0].w, q[step][1].w, kb.z, kb.w);
                         }
+                        // this thread's columns 2 t + (e & 1) of the tile are keys 32 m + 8 t + 4 (e & 1) + u of the page
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) s[4 * m + u][e] = acc[e] * p.scale2;
+                        for (int e = 0; e < 4; ++e)
+                            s[4 * m + u][e] = fmaf(acc[e], p.scale2, slope2[e >> 1] * (float)(key_base + 32 * m + 8 * t + 4 * (e & 1) + u - hi_key));
                     }
             }
             __syncwarp();
@@ -318,7 +322,7 @@ FRB_API int frb_attention_decode_tma(const void* q, const void* k_pages, const v
                                      const int* page_table, int max_pages, const int* seq_pos, const int* seq_slot,
                                      float* part_o, float* part_ml, void* out, int num_seqs, int num_heads, int num_kv_heads,
                                      int head_dim, float scale, int window, int max_chunks, int chunks_per_block, int* status,
-                                     cudaStream_t stream) {
+                                     const float* slopes, cudaStream_t stream) {
     if (num_seqs == 0) return 0;
     const int group = num_kv_heads > 0 ? num_heads / num_kv_heads : 0;
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0 && group <= 16,
@@ -337,7 +341,7 @@ FRB_API int frb_attention_decode_tma(const void* q, const void* k_pages, const v
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages; p.page_table = page_table;
     p.seq_pos = seq_pos; p.seq_slot = seq_slot; p.part_o = part_o; p.part_ml = part_ml; p.out = (bf16*)out;
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
-    p.num_kv_heads = num_kv_heads; p.max_chunks = parts; p.status = status;
+    p.num_kv_heads = num_kv_heads; p.max_chunks = parts; p.status = status; p.slopes = slopes;
     params.chunks_per_block = chunks_per_block; params.status = status;
     static const int early = [] { const char* v = getenv("FIELDRUN_B200_ATTENTION_EARLY"); return !(v && v[0] == '0'); }();
     params.early = early;

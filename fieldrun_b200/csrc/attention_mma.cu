@@ -5,10 +5,10 @@
 FRB_API int frb_attention_decode_mma(const void* q, const void* k_pages, const void* v_pages, const int* page_table,
                                      int max_pages, const int* seq_pos, const int* seq_slot, float* part_o, float* part_ml,
                                      void* out, int num_seqs, int num_heads, int num_kv_heads, int head_dim, float scale,
-                                     int window, int max_chunks, int* status, cudaStream_t stream) {
+                                     int window, int max_chunks, int* status, const float* slopes, cudaStream_t stream) {
     return launch_attention_decode("attention_decode_mma", q, k_pages, v_pages, page_table, max_pages, seq_pos, seq_slot,
                                    part_o, part_ml, out, num_seqs, num_heads, num_kv_heads, head_dim, scale, window,
-                                   max_chunks, stream, status);
+                                   max_chunks, stream, status, slopes);
 }
 
 // ----------------------------------------------------------------------------- many tokens per sequence
@@ -27,6 +27,7 @@ struct PrefillAttnParams {
     bf16* out;                 // [T, nh * HD]
     float scale2;
     int window, max_pages, num_heads, num_kv_heads;
+    const float* slopes;       // null, or one slope per query head: key j's score is lowered by slope * (position - j)
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -78,6 +79,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS <= 6 ? 2 : 1) attent
         const int head = kvh * group + (active ? hl : 0);
         RowTile<HD> st;
         tile_init(st);
+        const float slope2 = p.slopes ? p.slopes[head] * 1.4426950408889634f : 0.f;
 #pragma unroll
         for (int r = 0; r < 2; ++r)
             load_q_row(st, r, (active && valid[r]) ? p.q + ((size_t)(tok0 + g + 8 * r) * p.num_heads + head) * HD : nullptr, t);
@@ -97,7 +99,7 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS <= 6 ? 2 : 1) attent
             __syncthreads();
             if (active) {
                 const SharedPage<HD> page = {stages + cur * 2 * TILE, stages + cur * 2 * TILE + TILE};
-                tile_page(st, page, page_index * FRB_PAGE, lo, hi, p.scale2, g, t);
+                tile_page(st, page, page_index * FRB_PAGE, lo, hi, p.scale2, g, t, slope2);
             }
             __syncthreads();                            // the stage is free for the page after the next
         }
@@ -119,7 +121,7 @@ FRB_API int frb_attention_prefill_mma(const void* q, const void* k_pages, const 
                                       int max_pages, const int* tile_seq, const int* tile_q0, int num_tiles,
                                       const int* seq_slot, const int* seq_start, const int* seq_q_len, const int* cu_q_len,
                                       void* out, int num_heads, int num_kv_heads, int head_dim, float scale, int window,
-                                      cudaStream_t stream) {
+                                      const float* slopes, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0, "attention: %d heads over %d kv heads", num_heads, num_kv_heads);
     FRB_CHECK_ARG(head_dim == 32 || head_dim == 64 || head_dim == 96 || head_dim == 128,
@@ -129,7 +131,7 @@ FRB_API int frb_attention_prefill_mma(const void* q, const void* k_pages, const 
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages; p.page_table = page_table;
     p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_slot = seq_slot; p.seq_start = seq_start; p.seq_q_len = seq_q_len;
     p.cu_q_len = cu_q_len; p.out = (bf16*)out; p.scale2 = scale * 1.4426950408889634f; p.window = window;
-    p.max_pages = max_pages; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads;
+    p.max_pages = max_pages; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.slopes = slopes;
     const int group = num_heads / num_kv_heads;
     const int nwarps = group < 8 ? group : 8;
     dim3 grid(num_tiles, num_kv_heads);

@@ -84,10 +84,11 @@ struct SharedPage {
 };
 
 // Adds one page of 64 keys to the tile.  key_base: position of the page's first key; row r sees keys
-// lo[r] <= j <= hi[r].  scale2 = softmax scale * log2(e).
+// lo[r] <= j <= hi[r].  scale2 = softmax scale * log2(e).  slope2 = the head's distance slope * log2(e): the score
+// of key j for the query at position hi[r] is lowered by slope * (hi[r] - j); 0 for none.
 template <int HD, typename Page>
 __device__ __forceinline__ void tile_page(RowTile<HD>& st, const Page& page, int key_base, const int (&lo)[2],
-                                          const int (&hi)[2], float scale2, int g, int t) {
+                                          const int (&hi)[2], float scale2, int g, int t, float slope2 = 0.f) {
     float s[8][4];
     // scores: column block 4 m + u, column c = 2 t' + d of it stands for key 32 m + 8 t' + 2 u + d
 #pragma unroll
@@ -115,7 +116,7 @@ __device__ __forceinline__ void tile_page(RowTile<HD>& st, const Page& page, int
             for (int e = 0; e < 4; ++e) {
                 const int r = e >> 1;
                 const int key = key_base + 32 * m + 8 * t + 2 * u + (e & 1);
-                const float v = (key >= lo[r] && key <= hi[r]) ? s[4 * m + u][e] * scale2 : -INFINITY;
+                const float v = (key >= lo[r] && key <= hi[r]) ? fmaf(s[4 * m + u][e], scale2, slope2 * (float)(key - hi[r])) : -INFINITY;
                 s[4 * m + u][e] = v;
                 mx[r] = fmaxf(mx[r], v);
             }
@@ -186,7 +187,14 @@ struct DecodeAttnParams {
     float scale2;
     int window, max_pages, num_heads, num_kv_heads, max_chunks;
     int* status;               // null, or a word that gets FRB_STATUS_TOO_LONG when a sequence has more chunks than max_chunks
+    const float* slopes;       // null, or one slope per query head: key j's score is lowered by slope * (position - j)
 };
+
+// The slopes of the two query heads that a thread's rows g and g + 8 of the group's tile stand for, times log2(e).
+__device__ __forceinline__ void group_slopes(const float* slopes, int first_head, int group, int g, float (&slope2)[2]) {
+    slope2[0] = (slopes && g < group) ? slopes[first_head + g] * 1.4426950408889634f : 0.f;
+    slope2[1] = (slopes && g + 8 < group) ? slopes[first_head + g + 8] * 1.4426950408889634f : 0.f;
+}
 
 #define FRB_STATUS_TOO_LONG 5
 
@@ -214,6 +222,8 @@ __global__ void __launch_bounds__(128, 4) attention_decode_mma_kernel(DecodeAttn
         const size_t at = ((size_t)page * p.num_kv_heads + kvh) * FRB_PAGE * HD;
         const GlobalPage<HD> operands = {p.k_pages + at, p.v_pages + at};
         float s[8][4];
+        float slope2[2];
+        group_slopes(p.slopes, kvh * group, group, g, slope2);
         {
             const bf16* q_base = p.q + ((size_t)b * p.num_heads + (size_t)kvh * group) * HD;
             const bf16* q0 = g < group ? q_base + (size_t)g * HD : nullptr;
@@ -239,7 +249,7 @@ __global__ void __launch_bounds__(128, 4) attention_decode_mma_kernel(DecodeAttn
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
                         const int key = key_base + 32 * m + 8 * t + 2 * u + (e & 1);
-                        const float v = (key >= lo_key && key <= hi_key) ? acc[e] * p.scale2 : -INFINITY;
+                        const float v = (key >= lo_key && key <= hi_key) ? fmaf(acc[e], p.scale2, slope2[e >> 1] * (float)(key - hi_key)) : -INFINITY;
                         s[4 * m + u][e] = v;
                         row_max[e >> 1] = fmaxf(row_max[e >> 1], v);
                     }
@@ -378,7 +388,7 @@ static inline int launch_attention_decode(const char* what, const void* q, const
                                           const int* page_table, int max_pages, const int* seq_pos, const int* seq_slot,
                                           float* part_o, float* part_ml, void* out, int num_seqs, int num_heads,
                                           int num_kv_heads, int head_dim, float scale, int window, int max_chunks,
-                                          cudaStream_t stream, int* status = nullptr) {
+                                          cudaStream_t stream, int* status = nullptr, const float* slopes = nullptr) {
     if (num_seqs == 0) return 0;
     const int group = num_kv_heads > 0 ? num_heads / num_kv_heads : 0;
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0 && group <= 16,
@@ -390,7 +400,7 @@ static inline int launch_attention_decode(const char* what, const void* q, const
     p.q = (const bf16*)q; p.k_pages = (const bf16*)k_pages; p.v_pages = (const bf16*)v_pages; p.page_table = page_table;
     p.seq_pos = seq_pos; p.seq_slot = seq_slot; p.part_o = part_o; p.part_ml = part_ml; p.out = (bf16*)out;
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
-    p.num_kv_heads = num_kv_heads; p.max_chunks = max_chunks; p.status = status;
+    p.num_kv_heads = num_kv_heads; p.max_chunks = max_chunks; p.status = status; p.slopes = slopes;
     dim3 grid(max_chunks, num_kv_heads, num_seqs), merge_grid(num_heads, num_seqs);
 #define FRB_LAUNCH_DECODE(HD)                                                       \
     launch_dependent(attention_decode_mma_kernel<HD>, dim3(grid), dim3(128), 0, stream, p);                   \

@@ -85,10 +85,14 @@ struct AttnTcParams {
     int* status;
     float scale2;              // softmax scale * log2(e)
     int window, max_pages, num_heads, num_kv_heads;
+    const float* slopes;       // SLOPED kernels: one slope per query head; key j's score is lowered by slope * (i - j)
 };
 
-// grid (tile of 128 queries, head); the longest tiles of a sequence (its last ones) start first
-template <int HD>
+// grid (tile of 128 queries, head); the longest tiles of a sequence (its last ones) start first.
+// SLOPED: the scores carry a bias that falls with the distance between query and key (one more multiply-add on each
+// pair of scores; a page's maximum is then bounded from above by its largest score with the bias of its last key,
+// which is all the running maximum needs to be).
+template <int HD, bool SLOPED>
 __global__ void __launch_bounds__(AT_THREADS)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                             const __grid_constant__ CUtensorMap map_v, AttnTcParams p) {
@@ -225,6 +229,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const bool valid = q0 + row < q_len;
         const int hi = valid ? start + q0 + row : -1;
         const int lo = (valid && p.window > 0) ? max(0, hi - p.window + 1) : 0;
+        const float slope2 = SLOPED ? p.slopes[head] * 1.4426950408889634f : 0.f;
         float m_used = -INFINITY, l_sum = 0.f;
         bool ok = true, begun = false;
         for (int j = 0; j < num_steps; ++j) {
@@ -240,6 +245,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // Most pages lie wholly before the tile's first query (and inside the window): no key of theirs is
             // masked for any row of this warp, and the per-key comparisons are left out.
             const bool open_page = __all_sync(0xffffffffu, valid && key0 + FRB_PAGE - 1 <= hi && key0 >= lo);
+            const float bias0 = SLOPED ? slope2 * (float)(key0 - hi) : 0.f;      // the bias of the page's first key for this row
             float step_max;
             if (open_page) {
                 float top[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};     // four chains: a single one waits on itself
@@ -249,6 +255,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                     for (int i = 0; i < 16; i += 2)
                         top[(i >> 1) & 3] = max3(top[(i >> 1) & 3], __uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1]));
                 step_max = fmaxf(fmaxf(top[0], top[1]), fmaxf(top[2], top[3])) * p.scale2;     // the scale is positive
+                if (SLOPED) step_max += bias0 + slope2 * (float)(FRB_PAGE - 1);                // the bias grows with the key
             } else {
                 step_max = -INFINITY;
 #pragma unroll
@@ -258,7 +265,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
                         const int key = key0 + 16 * c + i;
                         const float v = key >= lo && key <= hi ? __uint_as_float(raw[c][i]) : -INFINITY;
                         raw[c][i] = __float_as_uint(v);
-                        step_max = fmaxf(step_max, v * p.scale2);
+                        step_max = fmaxf(step_max, SLOPED ? fmaf(v, p.scale2, bias0 + slope2 * (float)(16 * c + i)) : v * p.scale2);
                     }
             }
             float corr = 1.f;
@@ -269,7 +276,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
             // (a masked key gives 2^-inf = 0), one addition of the pair into one of four running pairs of sums.  (The
             // softmax is bound by the instructions it issues: a cubic on the multiply-add pipe for part of the
             // exponentials, to spare the special-function unit, made the kernel slower.)
-            const uint64_t scale_pair = pair_of(p.scale2, p.scale2), shift_pair = pair_of(-m_sub, -m_sub);
+            const uint64_t scale_pair = pair_of(p.scale2, p.scale2), shift_pair = pair_of(bias0 - m_sub, bias0 - m_sub);
+            const uint64_t slope_pair = pair_of(slope2, slope2);
             uint64_t sums[4] = {0ull, 0ull, 0ull, 0ull};
             uint32_t packed[FRB_PAGE / 32][16];
 #pragma unroll
@@ -277,7 +285,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
 #pragma unroll
                 for (int i = 0; i < 16; i += 2) {
                     float x0, x1;
-                    halves_of(fma_pairs(pair_of(__uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1])), scale_pair, shift_pair), x0, x1);
+                    const uint64_t shift = SLOPED ? fma_pairs(pair_of((float)(16 * c + i), (float)(16 * c + i + 1)), slope_pair, shift_pair)
+                                                  : shift_pair;
+                    halves_of(fma_pairs(pair_of(__uint_as_float(raw[c][i]), __uint_as_float(raw[c][i + 1])), scale_pair, shift), x0, x1);
                     const float a = exp2_fast(x0), bb = exp2_fast(x1);
                     sums[(i >> 1) & 3] = add_pairs(sums[(i >> 1) & 3], pair_of(a, bb));
                     packed[c >> 1][(c & 1) * 8 + (i >> 1)] = pack_bf16x2(a, bb);
@@ -377,7 +387,7 @@ FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* 
                                      const int* page_table, int max_pages, const int* tile_seq, const int* tile_q0,
                                      int num_tiles, const int* seq_slot, const int* seq_start, const int* seq_q_len,
                                      const int* cu_q_len, void* out, int num_heads, int num_kv_heads, int head_dim, float scale,
-                                     int window, int* status, cudaStream_t stream) {
+                                     int window, int* status, const float* slopes, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     FRB_CHECK_ARG(head_dim == 64 || head_dim == 128, "tensor-core attention: head_dim %d is neither 64 nor 128", head_dim);
     FRB_CHECK_ARG(scale > 0.f, "tensor-core attention: a softmax scale of %g is not positive", (double)scale);
@@ -393,15 +403,19 @@ FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* 
     p.page_table = page_table; p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_slot = seq_slot; p.seq_start = seq_start;
     p.seq_q_len = seq_q_len; p.cu_q_len = cu_q_len; p.out = (bf16*)out; p.status = status;
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
-    p.num_kv_heads = num_kv_heads;
+    p.num_kv_heads = num_kv_heads; p.slopes = slopes;
     const size_t smem = (size_t)AT_QUERIES * head_dim * 2 + (size_t)AT_STAGES * AT_STEP_PAGES * 2 * FRB_PAGE * head_dim * 2 + 1024;
     dim3 grid(num_tiles, num_heads);
+#define FRB_LAUNCH_TC(HD, SLOPED)                                                                                            \
+    do {                                                                                                                     \
+        cudaFuncSetAttribute(attention_prefill_tc_kernel<HD, SLOPED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_dependent(attention_prefill_tc_kernel<HD, SLOPED>, grid, dim3(AT_THREADS), smem, stream, map_q, map_k, map_v, p); \
+    } while (0)
     if (head_dim == 128) {
-        cudaFuncSetAttribute(attention_prefill_tc_kernel<128>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_dependent(attention_prefill_tc_kernel<128>, grid, dim3(AT_THREADS), smem, stream, map_q, map_k, map_v, p);
+        if (slopes) FRB_LAUNCH_TC(128, true); else FRB_LAUNCH_TC(128, false);
     } else {
-        cudaFuncSetAttribute(attention_prefill_tc_kernel<64>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_dependent(attention_prefill_tc_kernel<64>, grid, dim3(AT_THREADS), smem, stream, map_q, map_k, map_v, p);
+        if (slopes) FRB_LAUNCH_TC(64, true); else FRB_LAUNCH_TC(64, false);
     }
+#undef FRB_LAUNCH_TC
     FRB_RETURN_LAUNCH("attention_prefill_tc");
 }

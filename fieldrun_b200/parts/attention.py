@@ -157,11 +157,11 @@ class GQAAttention(Mixer):
 
     def attend(self, ctx, q: torch.Tensor, line: LineView, out: torch.Tensor) -> None:
         """Tensor-core kernels for bfloat16 and head sizes of 32, 64, 96 or 128 (tcgen05 for prompts with head
-        sizes 64 and 128, mma.sync otherwise); the general kernel for everything else."""
+        sizes 64 and 128, mma.sync otherwise), keys and values of one size; the general kernel for everything else.
+        All of them take the distance slopes."""
         common = dict(num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
-                      scale=self.softmax_scale, window=self.window)
-        plain = self.slopes is None and self.value_dim == self.head_dim
-        if plain and self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
+                      scale=self.softmax_scale, window=self.window, slopes=self.slopes)
+        if self.value_dim == self.head_dim and self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
             if ctx.is_decode and self.num_heads // self.num_kv_heads <= 16:
                 chunks = (ctx.max_kv_len + ops.ATTENTION_CHUNK - 1) // ops.ATTENTION_CHUNK
                 part_o = ctx.buffer("attention.part_o", (ctx.num_seqs, self.num_heads, chunks, self.head_dim), torch.float32)
@@ -181,8 +181,7 @@ class GQAAttention(Mixer):
                                           ctx.seq_start, ctx.seq_q_len, ctx.cu_q_len, out, **common)
             return
         ops.attention_generic(q, line.keys, line.values, line.page_table, ctx.tok_pos, ctx.tok_slot, out,
-                              num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
-                              scale=self.softmax_scale, window=self.window, v_dim=self.value_dim, slopes=self.slopes)
+                              v_dim=self.value_dim, **common)
 
 
 register_part("mixer", "gqa_attention", GQAAttention, replace=True)
