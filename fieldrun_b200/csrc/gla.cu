@@ -13,14 +13,26 @@
 // ((p + n) & 1) after its n tokens.  A step of one token therefore never writes what it reads, so a recorded step
 // that holds a sequence twice computes the same bits in both rows.
 //
-// This file has the scan that serves any sizes: one block per (sequence, head) walks the sequence's new tokens in
-// order, a prompt's or a single one.  A thread owns a value column v and a run of key channels and keeps its part of
-// the state in registers; tokens are taken sixteen at a time: their q, k, alpha and v are prepared in shared memory by
-// the whole block, the sixteen steps then run without a barrier, and the block finishes their outputs together.
+// One kernel serves a prompt's tokens and a single token.  A block takes a (work item, head): the item is a sequence's
+// new tokens, or a segment of them.  A warp owns a run of key channels, a lane VP value columns (v = lane + 32 j), and
+// each thread keeps its 64 elements of the state in registers; tokens are taken sixteen at a time: their q, k, alpha
+// and v are prepared in shared memory by the whole block, the sixteen steps then run without a barrier (three
+// broadcast loads for 2 VP multiply-adds on each channel), and the block finishes their outputs together.
+//
+// A long prompt alone would leave most of the device idle (one block per sequence and head, its tokens in order), so
+// its tokens are cut into segments that run side by side, in three launches:
+//   1. every segment from a zero state: its own contribution U = sum_j diag(prod_{s>j} alpha_s) k_j v_j^T and the
+//      product D of its decays (as the exponential of the summed logarithms);
+//   2. per sequence, head and state element, over the segments in order: the state at each segment's start,
+//      S <- D S + U, and the sequence's new state into the cache;
+//   3. every segment again from its start state, now with outputs.
+// The sums are those of the plain recurrence in another order, all in float32.
 #include "common.cuh"
 
 #define GLA_TOKENS 16        // tokens prepared together
-#define GLA_CHANNELS 64      // most key channels of the state that one thread keeps
+#define GLA_STATE_REGS 64    // elements of the state that one thread keeps
+
+enum { GLA_WHOLE = 0, GLA_LOCAL = 1, GLA_OUTPUT = 3 };
 
 struct GlaParams {
     const float* proj;       // [T, P]: q | k | v | g | a1 at the offsets below
@@ -32,10 +44,17 @@ struct GlaParams {
     const int* seq_start;    // [B] position of the sequence's first new token
     const int* cu_q_len;     // [B + 1] rows of the step before each sequence
     void* out;               // [T, heads * vdim], OutT
+    const int* seg_seq;      // [items] null: item b is all new tokens of sequence b; else the segment's sequence,
+    const int* seg_begin;    //   its first token among the sequence's new tokens
+    const int* seg_end;      //   and one past its last
+    float* seg_local;        // [items, heads, dim, vdim] GLA_LOCAL writes U here
+    float* seg_decay;        // [items, heads, dim]       GLA_LOCAL writes D here
+    const float* seg_first;  // [items, heads, dim, vdim] GLA_OUTPUT starts from here
     float inv_tau, q_scale, eps;
     int P, off_q, off_k, off_v, off_g, off_a;
     int heads, dim, vdim, rank;
-    int vpad, dsplit, dchunk;   // threads are [dsplit][vpad]; a thread keeps dchunk channels
+    int mode;
+    int vpad, dpad, parts, dchunk;   // a block is `parts` warps; a warp keeps dchunk channels; dpad = parts * dchunk
 };
 
 __device__ __forceinline__ float log_sigmoid(float z) {
@@ -43,42 +62,53 @@ __device__ __forceinline__ float log_sigmoid(float z) {
     return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
-template <typename WT, typename OutT>
+template <typename WT, typename OutT, int VP>
 __global__ void gla_scan_kernel(GlaParams p) {
+    constexpr int DC = GLA_STATE_REGS / VP;
     extern __shared__ float sm[];
     after_previous_kernel();
-    const int b = blockIdx.x, h = blockIdx.y;
+    const int item = blockIdx.x, h = blockIdx.y;
     const int dim = p.dim, vdim = p.vdim, rank = p.rank;
-    const int vpad = p.vpad, dsplit = p.dsplit, dchunk = p.dchunk;
+    const int vpad = p.vpad, dpad = p.dpad, parts = p.parts, dchunk = p.dchunk;
     const int nthreads = blockDim.x;
-    float* s_q = sm;                                   // [GLA_TOKENS][dim]
-    float* s_k = s_q + GLA_TOKENS * dim;
-    float* s_a = s_k + GLA_TOKENS * dim;
-    float* s_v = s_a + GLA_TOKENS * dim;               // [GLA_TOKENS][vdim]
-    float* s_a1 = s_v + GLA_TOKENS * vdim;             // [GLA_TOKENS][rank]
-    float* s_o = s_a1 + GLA_TOKENS * rank;             // [GLA_TOKENS][dsplit][vpad]
+    float* s_q = sm;                                   // [GLA_TOKENS][dpad]
+    float* s_k = s_q + GLA_TOKENS * dpad;
+    float* s_a = s_k + GLA_TOKENS * dpad;
+    float* s_v = s_a + GLA_TOKENS * dpad;              // [GLA_TOKENS][vpad]
+    float* s_a1 = s_v + GLA_TOKENS * vpad;             // [GLA_TOKENS][rank]
+    float* s_o = s_a1 + GLA_TOKENS * rank;             // [GLA_TOKENS][parts][vpad]
+    float* s_logsum = s_o + GLA_TOKENS * parts * vpad; // [dpad]
 
-    const int row0 = p.cu_q_len[b], n = p.cu_q_len[b + 1] - row0;
+    const int b = p.seg_seq ? p.seg_seq[item] : item;
+    const int row0 = p.cu_q_len[b], n_all = p.cu_q_len[b + 1] - row0;
+    const int t_begin = p.seg_seq ? p.seg_begin[item] : 0, t_end = p.seg_seq ? p.seg_end[item] : n_all;
     const int start = p.seq_start[b];
     const size_t slot = (size_t)p.seq_slot[b];
     const size_t head_state = (size_t)dim * vdim;
-    const float* s_in = p.state + ((slot * 2 + (start & 1)) * p.heads + h) * head_state;
-    float* s_out = p.state + ((slot * 2 + ((start + n) & 1)) * p.heads + h) * head_state;
+    const float* s_in = nullptr;
+    if (p.mode == GLA_WHOLE) s_in = p.state + ((slot * 2 + (start & 1)) * p.heads + h) * head_state;
+    else if (p.mode == GLA_OUTPUT) s_in = p.seg_first + ((size_t)item * p.heads + h) * head_state;
 
-    const int v = threadIdx.x % vpad, part = threadIdx.x / vpad;
+    const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
     const int d0 = part * dchunk;
-    const bool owner = v < vdim && part < dsplit;
-    float S[GLA_CHANNELS];
+    float S[DC][VP];
 #pragma unroll
-    for (int i = 0; i < GLA_CHANNELS; ++i)
-        S[i] = (owner && i < dchunk && d0 + i < dim) ? s_in[(size_t)(d0 + i) * vdim + v] : 0.f;
+    for (int i = 0; i < DC; ++i)
+#pragma unroll
+        for (int j = 0; j < VP; ++j) {
+            const int d = d0 + i, v = lane + 32 * j;
+            S[i][j] = (s_in && i < dchunk && d < dim && v < vdim) ? s_in[(size_t)d * vdim + v] : 0.f;
+        }
+    for (int i = threadIdx.x; i < dpad; i += nthreads) s_logsum[i] = 0.f;
+    // the padding of the rows stays zero: q = k = alpha = 0 there keeps a padded element of the state at zero
+    for (int i = threadIdx.x; i < GLA_TOKENS * dpad; i += nthreads) { s_q[i] = 0.f; s_k[i] = 0.f; s_a[i] = 0.f; }
+    for (int i = threadIdx.x; i < GLA_TOKENS * vpad; i += nthreads) s_v[i] = 0.f;
 
     const WT* a2 = (const WT*)p.a2 + (size_t)h * dim * rank;
     const float* a2_bias = p.a2_bias + h * dim;
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = nthreads >> 5;
 
-    for (int t0 = 0; t0 < n; t0 += GLA_TOKENS) {
-        const int count = min(GLA_TOKENS, n - t0);
+    for (int t0 = t_begin; t0 < t_end; t0 += GLA_TOKENS) {
+        const int count = min(GLA_TOKENS, t_end - t0);
         const float* rows = p.proj + (size_t)(row0 + t0) * p.P;
         __syncthreads();                               // the outputs of the tokens before are finished
         for (int i = threadIdx.x; i < count * rank; i += nthreads) {
@@ -87,12 +117,12 @@ __global__ void gla_scan_kernel(GlaParams p) {
         }
         for (int i = threadIdx.x; i < count * vdim; i += nthreads) {
             const int t = i / vdim, c = i - t * vdim;
-            s_v[i] = rows[(size_t)t * p.P + p.off_v + h * vdim + c];
+            s_v[t * vpad + c] = rows[(size_t)t * p.P + p.off_v + h * vdim + c];
         }
         for (int i = threadIdx.x; i < count * dim; i += nthreads) {
             const int t = i / dim, d = i - t * dim;
-            s_q[i] = rows[(size_t)t * p.P + p.off_q + h * dim + d] * p.q_scale;
-            s_k[i] = rows[(size_t)t * p.P + p.off_k + h * dim + d];
+            s_q[t * dpad + d] = rows[(size_t)t * p.P + p.off_q + h * dim + d] * p.q_scale;
+            s_k[t * dpad + d] = rows[(size_t)t * p.P + p.off_k + h * dim + d];
         }
         __syncthreads();
         for (int i = threadIdx.x; i < count * dim; i += nthreads) {
@@ -101,34 +131,53 @@ __global__ void gla_scan_kernel(GlaParams p) {
             const WT* w = a2 + (size_t)d * rank;
             const float* a1 = s_a1 + t * rank;
             for (int r = 0; r < rank; ++r) z += to_f32<WT>(w[r]) * a1[r];
-            s_a[i] = expf(log_sigmoid(z) * p.inv_tau);
+            s_a[t * dpad + d] = log_sigmoid(z) * p.inv_tau;          // the decay's logarithm, for now
         }
         __syncthreads();
-        if (owner) {
-            for (int t = 0; t < count; ++t) {
-                const float* q = s_q + t * dim + d0;
-                const float* k = s_k + t * dim + d0;
-                const float* a = s_a + t * dim + d0;
-                const float vt = s_v[t * vdim + v];
-                float o = 0.f;
+        if (p.mode == GLA_LOCAL)
+            for (int d = threadIdx.x; d < dim; d += nthreads) {
+                float sum = s_logsum[d];
+                for (int t = 0; t < count; ++t) sum += s_a[t * dpad + d];
+                s_logsum[d] = sum;
+            }
+        __syncthreads();
+        for (int i = threadIdx.x; i < count * dim; i += nthreads) {
+            const int t = i / dim, d = i - t * dim;
+            s_a[t * dpad + d] = expf(s_a[t * dpad + d]);
+        }
+        __syncthreads();
+        for (int t = 0; t < count; ++t) {
+            const float* q = s_q + t * dpad + d0;
+            const float* k = s_k + t * dpad + d0;
+            const float* a = s_a + t * dpad + d0;
+            float vt[VP], o[VP];
 #pragma unroll
-                for (int i = 0; i < GLA_CHANNELS; ++i) {
-                    if (i < dchunk && d0 + i < dim) {
-                        S[i] = a[i] * S[i] + k[i] * vt;
-                        o += q[i] * S[i];
+            for (int j = 0; j < VP; ++j) { vt[j] = s_v[t * vpad + lane + 32 * j]; o[j] = 0.f; }
+#pragma unroll
+            for (int i = 0; i < DC; ++i) {
+                if (i < dchunk) {
+                    const float ai = a[i], ki = k[i], qi = q[i];
+#pragma unroll
+                    for (int j = 0; j < VP; ++j) {
+                        S[i][j] = ai * S[i][j] + ki * vt[j];
+                        o[j] += qi * S[i][j];
                     }
                 }
-                s_o[(t * dsplit + part) * vpad + v] = o;
+            }
+            if (p.mode != GLA_LOCAL) {
+#pragma unroll
+                for (int j = 0; j < VP; ++j) s_o[(t * parts + part) * vpad + lane + 32 * j] = o[j];
             }
         }
+        if (p.mode == GLA_LOCAL) continue;
         __syncthreads();
         // a warp finishes a token: the parts of o added in order, the head's root mean square, weight and gate
-        for (int t = warp; t < count; t += nwarps) {
+        for (int t = part; t < count; t += parts) {
             float ss = 0.f;
             for (int c = lane; c < vdim; c += 32) {
                 float o = 0.f;
-                for (int s = 0; s < dsplit; ++s) o += s_o[(t * dsplit + s) * vpad + c];
-                s_o[(t * dsplit) * vpad + c] = o;
+                for (int s = 0; s < parts; ++s) o += s_o[(t * parts + s) * vpad + c];
+                s_o[(t * parts) * vpad + c] = o;
                 ss += o * o;
             }
             ss = warp_sum(ss);
@@ -137,45 +186,108 @@ __global__ void gla_scan_kernel(GlaParams p) {
             OutT* out = (OutT*)p.out + ((size_t)(row0 + t0 + t) * p.heads + h) * vdim;
             for (int c = lane; c < vdim; c += 32) {
                 const float gate = g[c];
-                out[c] = from_f32<OutT>(s_o[(t * dsplit) * vpad + c] * rinv * p.norm_w[c] * (gate / (1.0f + expf(-gate))));
+                out[c] = from_f32<OutT>(s_o[(t * parts) * vpad + c] * rinv * p.norm_w[c] * (gate / (1.0f + expf(-gate))));
             }
         }
     }
-    if (owner) {
+    if (p.mode == GLA_OUTPUT) return;
+    float* s_out = p.mode == GLA_WHOLE ? p.state + ((slot * 2 + ((start + n_all) & 1)) * p.heads + h) * head_state
+                                       : p.seg_local + ((size_t)item * p.heads + h) * head_state;
 #pragma unroll
-        for (int i = 0; i < GLA_CHANNELS; ++i)
-            if (i < dchunk && d0 + i < dim) s_out[(size_t)(d0 + i) * vdim + v] = S[i];
+    for (int i = 0; i < DC; ++i)
+#pragma unroll
+        for (int j = 0; j < VP; ++j) {
+            const int d = d0 + i, v = lane + 32 * j;
+            if (i < dchunk && d < dim && v < vdim) s_out[(size_t)d * vdim + v] = S[i][j];
+        }
+    if (p.mode == GLA_LOCAL) {
+        __syncthreads();
+        for (int d = threadIdx.x; d < dim; d += nthreads) p.seg_decay[((size_t)item * p.heads + h) * dim + d] = expf(s_logsum[d]);
     }
 }
 
+// Launch 2 of a segmented prompt.  grid (sequence, head, tiles of 256 state elements).
+__global__ void gla_combine_kernel(const float* __restrict__ seg_local, const float* __restrict__ seg_decay,
+                                   float* __restrict__ seg_first, float* state, const int* __restrict__ seq_slot,
+                                   const int* __restrict__ seq_start, const int* __restrict__ cu_q_len,
+                                   const int* __restrict__ seq_seg0, int heads, int dim, int vdim) {
+    const int b = blockIdx.x, h = blockIdx.y;
+    const int e = blockIdx.z * blockDim.x + threadIdx.x;
+    const int elements = dim * vdim;
+    if (e >= elements) return;
+    const int d = e / vdim;
+    const int first = seq_seg0[b], count = seq_seg0[b + 1] - first;
+    const int start = seq_start[b], n = cu_q_len[b + 1] - cu_q_len[b];
+    const size_t slot = (size_t)seq_slot[b];
+    float S = state[((slot * 2 + (start & 1)) * heads + h) * elements + e];
+#pragma unroll 4
+    for (int s = first; s < first + count; ++s) {
+        const size_t at = (size_t)s * heads + h;
+        seg_first[at * elements + e] = S;
+        S = seg_decay[at * dim + d] * S + seg_local[at * elements + e];
+    }
+    state[((slot * 2 + ((start + n) & 1)) * heads + h) * elements + e] = S;
+}
+
+// num_items = num_seqs and null tables: every sequence whole.  With tables: the three launches of a segmented prompt;
+// seg_scratch holds 2 * num_items * heads * dim * vdim + num_items * heads * dim floats.
 FRB_API int frb_gla_scan(const float* proj, int P, int off_q, int off_k, int off_v, int off_g, int off_a,
                          const void* a2, int weight_dtype, const float* a2_bias, const float* norm_w, float* state,
                          const int* seq_slot, const int* seq_start, const int* cu_q_len, void* out, int out_dtype,
                          int num_seqs, int heads, int dim, int vdim, int rank, float tau, float q_scale, float eps,
-                         cudaStream_t stream) {
+                         const int* seg_seq, const int* seg_begin, const int* seg_end, const int* seq_seg0, int num_items,
+                         float* seg_scratch, cudaStream_t stream) {
     if (num_seqs == 0) return 0;
     FRB_CHECK_ARG(dim >= 1 && vdim >= 1 && rank >= 1 && heads >= 1 && heads <= 65535, "gla: %d heads of %d x %d, rank %d",
                   heads, dim, vdim, rank);
     FRB_CHECK_ARG(tau > 0.f, "gla: tau %f", (double)tau);
+    FRB_CHECK_ARG(vdim <= 256, "gla: a value head of %d (at most 256)", vdim);
     GlaParams p;
     p.proj = proj; p.a2 = a2; p.a2_bias = a2_bias; p.norm_w = norm_w; p.state = state; p.seq_slot = seq_slot;
     p.seq_start = seq_start; p.cu_q_len = cu_q_len; p.out = out; p.inv_tau = 1.0f / tau; p.q_scale = q_scale; p.eps = eps;
     p.P = P; p.off_q = off_q; p.off_k = off_k; p.off_v = off_v; p.off_g = off_g; p.off_a = off_a;
     p.heads = heads; p.dim = dim; p.vdim = vdim; p.rank = rank;
     p.vpad = (vdim + 31) / 32 * 32;
-    FRB_CHECK_ARG(p.vpad <= 1024, "gla: a value head of %d", vdim);
-    int dsplit = (dim + GLA_CHANNELS - 1) / GLA_CHANNELS;
-    const int want = 256 / p.vpad;                       // about 256 threads where the sizes allow
-    if (dsplit < want) dsplit = want < dim ? want : dim;
-    FRB_CHECK_ARG(dsplit * p.vpad <= 1024, "gla: a state of %d x %d per head needs more than 1024 threads", dim, vdim);
-    p.dsplit = dsplit;
-    p.dchunk = (dim + dsplit - 1) / dsplit;
-    const size_t smem = ((size_t)GLA_TOKENS * (3 * dim + vdim + rank) + (size_t)GLA_TOKENS * dsplit * p.vpad) * sizeof(float);
+    int vp = p.vpad / 32;                                 // columns per lane: 1, 2, 4 or 8
+    if (vp == 3) vp = 4; else if (vp > 4) vp = 8;
+    p.vpad = 32 * vp;
+    const int most = GLA_STATE_REGS / vp;                 // channels a warp can keep
+    int parts = (dim + most - 1) / most;
+    if (parts < 8) parts = dim < 8 ? dim : 8;             // eight warps where the sizes allow
+    FRB_CHECK_ARG(parts <= 32, "gla: a state of %d x %d per head needs more than 1024 threads", dim, vdim);
+    p.parts = parts;
+    p.dchunk = (dim + parts - 1) / parts;
+    p.dpad = p.parts * p.dchunk;
+    const size_t smem = ((size_t)GLA_TOKENS * (3 * p.dpad + p.vpad + rank) + (size_t)GLA_TOKENS * parts * p.vpad + p.dpad) * sizeof(float);
     FRB_CHECK_ARG(smem <= 200 * 1024, "gla: %d x %d per head with rank %d needs more than 200 KB of shared memory", dim, vdim, rank);
+    const bool segmented = seg_seq != nullptr;
+    FRB_CHECK_ARG(!segmented || (seg_begin && seg_end && seq_seg0 && seg_scratch && num_items > 0), "gla: segment tables are incomplete");
+    const size_t per_item = (size_t)heads * dim * vdim;
+    p.seg_seq = seg_seq; p.seg_begin = seg_begin; p.seg_end = seg_end;
+    p.seg_local = segmented ? seg_scratch : nullptr;
+    float* seg_first = segmented ? seg_scratch + (size_t)num_items * per_item : nullptr;
+    p.seg_first = seg_first;
+    p.seg_decay = segmented ? seg_scratch + 2 * (size_t)num_items * per_item : nullptr;
+    const dim3 grid(segmented ? num_items : num_seqs, heads), block(32 * parts);
+#define FRB_GLA_LAUNCH(VP)                                                                                            \
+    do {                                                                                                              \
+        auto kernel = gla_scan_kernel<WT, OutT, VP>;                                                                  \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        if (!segmented) {                                                                                             \
+            p.mode = GLA_WHOLE;                                                                                       \
+            launch_dependent(kernel, grid, block, smem, stream, p);                                                   \
+        } else {                                                                                                      \
+            p.mode = GLA_LOCAL;                                                                                       \
+            kernel<<<grid, block, smem, stream>>>(p);                                                                 \
+            gla_combine_kernel<<<dim3(num_seqs, heads, (dim * vdim + 255) / 256), 256, 0, stream>>>(                  \
+                p.seg_local, p.seg_decay, seg_first, state, seq_slot, seq_start, cu_q_len, seq_seg0, heads, dim, vdim); \
+            p.mode = GLA_OUTPUT;                                                                                      \
+            kernel<<<grid, block, smem, stream>>>(p);                                                                 \
+        }                                                                                                             \
+    } while (0)
     FRB_DISPATCH_DTYPE(weight_dtype, WT, FRB_DISPATCH_DTYPE(out_dtype, OutT, {
-        auto kernel = gla_scan_kernel<WT, OutT>;
-        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        launch_dependent(kernel, dim3(num_seqs, heads), dim3(dsplit * p.vpad), smem, stream, p);
+        if (vp == 1) FRB_GLA_LAUNCH(1); else if (vp == 2) FRB_GLA_LAUNCH(2); else if (vp == 4) FRB_GLA_LAUNCH(4); else FRB_GLA_LAUNCH(8);
     }));
+#undef FRB_GLA_LAUNCH
     FRB_RETURN_LAUNCH("gla_scan");
 }

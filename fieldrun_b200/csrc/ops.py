@@ -29,7 +29,7 @@ _SIGNATURES = {
     "frb_layernorm": "ppppfppiii",
     "frb_unary_unit": "ppili",
     "frb_softcap": "plf",
-    "frb_gla_scan": "piiiiiipipppppppiiiiiifff",
+    "frb_gla_scan": "piiiiiipipppppppiiiiiifffppppip",
     "frb_router_topk": "ppiiiifpp",
     "frb_expert_plan": "piiiippppppp",
     "frb_expert_combine": "pppiiip",
@@ -246,18 +246,39 @@ def softcap(logits: torch.Tensor, cap: float) -> None:
 def gla_scan(proj: torch.Tensor, offsets: tuple[int, int, int, int, int], a2: torch.Tensor, a2_bias: torch.Tensor,
              norm_weight: torch.Tensor, state: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor,
              cu_q_len: torch.Tensor, out: torch.Tensor, *, heads: int, dim: int, vdim: int, tau: float, q_scale: float,
-             eps: float) -> None:
+             eps: float, segments: Optional[tuple[torch.Tensor, torch.Tensor, torch.Tensor, torch.Tensor]] = None,
+             scratch: Optional[torch.Tensor] = None) -> None:
     """Gated linear attention over the step's new tokens (see gla.cu): ``proj`` float32 [T, P] holds q, k, v, g and
-    the decay's inner rows at ``offsets``; ``state`` float32 [slots, 2, heads, dim, vdim]; ``out`` [T, heads * vdim]."""
+    the decay's inner rows at ``offsets``; ``state`` float32 [slots, 2, heads, dim, vdim]; ``out`` [T, heads * vdim].
+    ``segments`` = (sequence, first token, end token of every segment; first segment of every sequence and, last, the
+    number of segments), int32 on the device, cuts the sequences' new tokens into pieces that run side by side;
+    ``scratch`` then holds :func:`gla_scratch_floats` float32."""
     _want(proj, torch.float32, "projected rows")
     _want(state, torch.float32, "the recurrent state")
     _want(a2_bias, torch.float32, "the decay's bias")
     _want(norm_weight, torch.float32, "the output norm's weight")
     if tuple(state.shape[1:]) != (2, heads, dim, vdim):
         raise KernelError(f"the recurrent state is {list(state.shape)}, not [slots, 2, {heads}, {dim}, {vdim}]")
+    seg = (None, None, None, None)
+    items = seq_slot.numel()
+    if segments is not None:
+        seg = segments
+        items = seg[0].numel()
+        for t in seg:
+            _want(t, torch.int32, "segment tables")
+        if seg[3].numel() != seq_slot.numel() + 1:
+            raise KernelError("the table of the sequences' first segments needs one entry per sequence and one more")
+        if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < gla_scratch_floats(items, heads, dim, vdim):
+            raise KernelError("a segmented scan needs float32 scratch of gla_scratch_floats(...) elements")
     _call("frb_gla_scan", _ptr(proj), proj.shape[1], *[int(o) for o in offsets], _ptr(a2), _code(a2.dtype), _ptr(a2_bias),
           _ptr(norm_weight), _ptr(state), _ptr(seq_slot), _ptr(seq_start), _ptr(cu_q_len), _ptr(out), _code(out.dtype),
-          seq_slot.numel(), heads, dim, vdim, a2.shape[1], float(tau), float(q_scale), float(eps))
+          seq_slot.numel(), heads, dim, vdim, a2.shape[1], float(tau), float(q_scale), float(eps),
+          _ptr(seg[0]), _ptr(seg[1]), _ptr(seg[2]), _ptr(seg[3]), items, _ptr(scratch) if segments is not None else None)
+
+
+def gla_scratch_floats(items: int, heads: int, dim: int, vdim: int) -> int:
+    """float32 elements of scratch that :func:`gla_scan` needs for ``items`` segments."""
+    return 2 * items * heads * dim * vdim + items * heads * dim
 
 
 NORM_MAX_SUMMED_ROWS = 32      # most weighted rows per token that the norm kernel sums itself (NORM_MAX_TOP_K)

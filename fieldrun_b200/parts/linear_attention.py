@@ -10,7 +10,8 @@ shared by the heads, the heads side by side are multiplied by silu(G x_t), and t
 The state starts at zero (the cache zeroes a slot's state when it hands the slot out) and is carried from step
 to step in the cache line's state area, which holds two copies per slot so that a step of one token reads one
 and writes the other (see gla.cu).  q, k, v, the gate and A1 x come from one product; everything between that
-product and the output projection is one kernel in float32.
+product and the output projection is one kernel in float32 (three launches of it for a long prompt, whose tokens
+are cut into segments that run side by side).
 """
 from __future__ import annotations
 
@@ -23,6 +24,9 @@ from ..csrc import ops
 from ..weights.loader import MATRIX, VECTOR, TensorNeed, TensorSource
 from .base import Mixer, register_part
 from .linear import linear
+
+
+SEGMENT_TOKENS = 128        # a long prompt's tokens run in segments of this many, side by side (see gla.cu)
 
 
 class GatedLinearAttention(Mixer):
@@ -83,14 +87,41 @@ class GatedLinearAttention(Mixer):
     def cache_need(self) -> CacheNeed:
         return CacheNeed(state_shape=(2, self.num_heads, self.head_dim, self.value_dim), state_dtype="float32")
 
+    def segments(self, ctx):
+        """Tables that cut the step's prompts into segments of ``SEGMENT_TOKENS``, or None when the sequences as they
+        are give the device enough blocks (or are short).  Only a step of prompts comes here, and such a step is never
+        recorded, so the lengths may be read on the host."""
+        if ctx.is_decode or ctx.max_q_len < 2 * SEGMENT_TOKENS:
+            return None
+        if ctx.num_seqs * self.num_heads >= 2 * ops.sm_count(ctx.device):
+            return None
+        cached = getattr(ctx, "_token_segments", None)          # the same for every recurrent layer of the step
+        if cached is None:
+            seqs, begins, ends, first = [], [], [], [0]
+            for b, n in enumerate(ctx.seq_q_lens):
+                for lo in range(0, n, SEGMENT_TOKENS):
+                    seqs.append(b)
+                    begins.append(lo)
+                    ends.append(min(lo + SEGMENT_TOKENS, n))
+                first.append(len(seqs))
+            flat = torch.tensor(seqs + begins + ends + first, dtype=torch.int32).to(ctx.device)
+            count = len(seqs)
+            cached = ctx._token_segments = (flat[:count], flat[count:2 * count], flat[2 * count:3 * count], flat[3 * count:])
+        return cached
+
     def forward(self, ctx, act: torch.Tensor, line: LineView, writes_cache: bool) -> torch.Tensor:
         if not writes_cache:
             raise ValueError("a recurrent layer cannot read another layer's state: it has to write its own")
         proj = linear(act, self.w_in)                                       # float32 [T, 2 qk + 2 v + rank]
         out = ctx.buffer("linear_attention.out", (act.shape[0], self.v_width), self.dtype)
+        segments = self.segments(ctx)
+        scratch = None
+        if segments is not None:
+            floats = ops.gla_scratch_floats(segments[0].numel(), self.num_heads, self.head_dim, self.value_dim)
+            scratch = ctx.buffer("linear_attention.segments", (floats,), torch.float32)
         ops.gla_scan(proj, self.offsets, self.w_decay, self.decay_bias, self.norm_weight, line.state, ctx.seq_slot,
                      ctx.seq_start, ctx.cu_q_len, out, heads=self.num_heads, dim=self.head_dim, vdim=self.value_dim,
-                     tau=self.tau, q_scale=self.q_scale, eps=self.norm_eps)
+                     tau=self.tau, q_scale=self.q_scale, eps=self.norm_eps, segments=segments, scratch=scratch)
         return linear(out, self.w_o)
 
 

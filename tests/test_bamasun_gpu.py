@@ -281,6 +281,52 @@ def test_gated_linear_attention_scan_with_state_carried_between_calls(heads, dim
         close(f64(state[slots[b], n & 1]), states[b], 2e-5, f"state of sequence {b}")
 
 
+@pytest.mark.parametrize("heads,dim,vdim,rank,tau", [(2, 16, 24, 5, 4.0), (1, 128, 128, 16, 16.0), (3, 40, 70, 3, 1.0)])
+def test_gated_linear_attention_in_segments_side_by_side(heads, dim, vdim, rank, tau):
+    """A first call leaves a state; the second call's tokens are cut into segments of 128, 50 and 1 tokens that
+    run side by side: outputs and the new state equal the plain recurrence over all tokens."""
+    rng = np.random.default_rng(dim * vdim)
+    width = 32
+    w, mixer = gla_case(rng, heads, dim, vdim, rank, width, tau, 1.0)
+    first, second = [70, 3, 1], [300, 129, 1]
+    h = [rng.normal(size=(a + b, width)) for a, b in zip(first, second)]
+    want, states = zip(*[pb.gla_mixer(x, w, "m.", mixer, 1e-5) for x in h])
+    w_in = dev(np.concatenate([w["m.q"], w["m.k"], w["m.v"], w["m.g"], w["m.a1"]]), torch.float32)
+    offsets = (0, heads * dim, 2 * heads * dim, 2 * heads * dim + heads * vdim, 2 * heads * dim + 2 * heads * vdim)
+    state = torch.zeros((4, 2, heads, dim, vdim), dtype=torch.float32, device=DEV)
+    slots = dev(np.array([2, 0, 3], dtype=np.int32))
+    tensors = (dev(w["m.a2"], torch.float32), dev(w["m.a2.b"], torch.float32), dev(w["m.norm"], torch.float32))
+    sizes = dict(heads=heads, dim=dim, vdim=vdim, tau=tau, q_scale=dim ** -0.5, eps=1e-5)
+    for call, lengths in enumerate((first, second)):
+        begin = [0, 0, 0] if call == 0 else first
+        rows = np.concatenate([x[b:b + n] for x, b, n in zip(h, begin, lengths)])
+        proj = torch.mm(dev(rows, torch.float32), w_in.t())
+        out = torch.empty((rows.shape[0], heads * vdim), dtype=torch.float32, device=DEV)
+        cu = np.concatenate([[0], np.cumsum(lengths)]).astype(np.int32)
+        segments = scratch = None
+        if call == 1:
+            for size in (128, 50, 1):
+                seqs, lo, hi, firsts = [], [], [], [0]
+                for b, n in enumerate(lengths):
+                    for t in range(0, n, size):
+                        seqs.append(b), lo.append(t), hi.append(min(t + size, n))
+                    firsts.append(len(seqs))
+                segments = tuple(dev(np.array(x, dtype=np.int32)) for x in (seqs, lo, hi, firsts))
+                scratch = torch.full((ops().gla_scratch_floats(len(seqs), heads, dim, vdim),), float("nan"), device=DEV)
+                kept = state.clone()
+                ops().gla_scan(proj, offsets, *tensors, kept, slots, dev(np.array(begin, dtype=np.int32)), dev(cu), out,
+                               segments=segments, scratch=scratch, **sizes)
+                o = f64(out)
+                for b, n in enumerate(lengths):
+                    close(o[cu[b]:cu[b + 1]], want[b][begin[b]:], 3e-5, f"segments of {size}, sequence {b}")
+                    close(f64(kept[int(slots[b]), (begin[b] + n) & 1]), states[b], 3e-5, f"segments of {size}, state {b}")
+        else:
+            ops().gla_scan(proj, offsets, *tensors, state, slots, dev(np.array(begin, dtype=np.int32)), dev(cu), out, **sizes)
+            o = f64(out)
+            for b, n in enumerate(lengths):
+                close(o[cu[b]:cu[b + 1]], want[b][:n], 3e-5, f"first call, sequence {b}")
+
+
 def test_gated_linear_attention_remembers_a_token_hundreds_of_steps_back():
     """With decays close to one the first token's value is still in the output 600 tokens later; with strong
     decays it is gone.  The first token alone carries a large key and value."""
