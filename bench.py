@@ -12,7 +12,8 @@ and out every step, `_e2e`), all three batch sizes again in mid-run (contexts of
 each with the bytes its step has to read and the fraction of the memory roofline, and (`long_cache`) a batch of
 8 sequences of 8,192 to 65,536 tokens: their prompts and decode steps over those caches.  With --gpus above 1
 it says that it is a single-GPU program and exits with 2.  `--impl reference` reports that the reference cannot
-run here.
+run here.  `--design bamasun` runs another workload instead and leaves the default one as it is: the Bamasun design
+beside MiniMax-M2 at equal sizes (see fieldrun_b200/compare.py).
 """
 from __future__ import annotations
 
@@ -121,6 +122,10 @@ def main() -> int:
     parser.add_argument("--skip-points", action="store_true", help="leave out prefill and the batch 1/64 points")
     parser.add_argument("--skip-long-cache", action="store_true", help="leave out the batch of 8,192 to 65,536 tokens")
     parser.add_argument("--skip-loop", action="store_true", help="leave out the generate_batch timings")
+    parser.add_argument("--design", default=None, choices=["bamasun"],
+                        help="instead of the default workload: this design beside MiniMax-M2 at equal sizes "
+                             "(prompt and decode throughput, every kernel of a step); see fieldrun_b200/compare.py")
+    parser.add_argument("--sizes", default="w2048,w4096", help="with --design: which of compare.SIZES, with commas between")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -133,6 +138,12 @@ def main() -> int:
         return 2
     if args.warmup < 3:
         args.warmup = 3
+    if args.design is not None:
+        from fieldrun_b200.compare import compare_designs
+        out = compare_designs(tuple(args.sizes.split(",")), steps=min(args.steps, 16), warmup=args.warmup)
+        out.update({"design": args.design, "n_gpus": 1, "peaks": peaks()[0], "peaks_source": peaks()[1]})
+        print(json.dumps(out))
+        return 0
 
     import numpy as np
     import torch

@@ -1,0 +1,145 @@
+"""Two designs side by side at equal sizes: prompt and decode throughput, and where a step's time goes.
+
+``python bench.py --design bamasun`` prints what :func:`compare_designs` returns.  For each size it builds a Bamasun
+model (attention, recurrent and key-sharing layers in turn, dense feed-forward) and a MiniMax-M2 model of the same
+width, heads, head size, layers and vocabulary whose feed-forward is a single expert of two thirds the width (three
+matrices instead of two: the same weights and multiply-adds), both with random weights in bfloat16, and measures
+
+* a step of prompts (tokens a second, CUDA events around the step, after warm-up steps);
+* decode steps at two batch sizes from those prompts (tokens a second; the tokens stay on the device);
+* every kernel of one prompt step and one decode step, timed alone with CUDA events (``ops.timing_start``), summed
+  by kernel name.
+
+The weights of every model are far larger than the L2 cache, and each timed step reads all of them.
+"""
+from __future__ import annotations
+
+import time
+from typing import Any
+
+import numpy as np
+import torch
+
+SIZES = {
+    # name: width, heads, kv heads, head size, feed-forward width, layers, vocabulary
+    "w2048": dict(width=2048, heads=16, kv_heads=4, dim=128, ff=8192, layers=8, vocab=32768),
+    "w4096": dict(width=4096, heads=32, kv_heads=8, dim=128, ff=14336, layers=4, vocab=32768),
+    "w1024": dict(width=1024, heads=16, kv_heads=2, dim=64, ff=4096, layers=8, vocab=32768),
+}
+PROMPT = 2048
+PROMPTS_PER_STEP = 4
+
+
+def bamasun_config(width, heads, kv_heads, dim, ff, layers, vocab) -> dict[str, Any]:
+    """Layers in turns of four: attention, recurrent, attention over the first one's keys and values, attention."""
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                 "q_temp": {"coef": 0.3, "every": 128}}
+    listed = []
+    for index in range(layers):
+        turn = index % 4
+        if turn == 1:
+            mixer = {"heads": heads, "dim": dim, "vdim": dim, "tau": 16.0, "rank": 32}
+            listed.append({"type": "gla", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+        else:
+            mixer = dict(attention)
+            if turn == 2:
+                mixer["kv_from"] = index - 2
+            listed.append({"type": "attention", "mixer": mixer, "mlp": {"kind": "dense", "ff": ff}})
+    return {"architecture": "Bamasun", "vocab": vocab, "width": width, "embedding": {"scale": 8.0}, "norm": {"eps": 1e-6},
+            "logit_softcap": 30.0, "layers": listed}
+
+
+def minimax_config(width, heads, kv_heads, dim, ff, layers, vocab) -> dict[str, Any]:
+    return dict(architectures=["MiniMaxM2ForCausalLM"], model_type="minimax_m2", hidden_size=width, num_attention_heads=heads,
+                num_key_value_heads=kv_heads, head_dim=dim, rotary_dim=dim // 2, rope_theta=1000000.0, use_qk_norm=True,
+                num_local_experts=1, num_experts_per_tok=1, intermediate_size=(2 * ff // 3 + 127) // 128 * 128,
+                vocab_size=vocab, rms_norm_eps=1e-6, tie_word_embeddings=False, num_hidden_layers=layers)
+
+
+def _measure(lm, vocab: int, steps: int, warmup: int, decode_batches=(8, 64)) -> dict[str, Any]:
+    from .csrc import ops
+    engine = lm.engine
+    rng = np.random.default_rng(0)
+
+    def prompts(n):
+        return [rng.integers(0, vocab, size=PROMPT).tolist() for _ in range(n)]
+
+    out: dict[str, Any] = {"weight_bytes": lm.model.weight_bytes()}
+    # ---- a step of prompts
+    times = []
+    for i in range(warmup + steps):
+        slots = [engine.new_sequence() for _ in range(PROMPTS_PER_STEP)]
+        batch = prompts(PROMPTS_PER_STEP)
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        start.record()
+        engine.step(slots, batch)
+        stop.record()
+        torch.cuda.synchronize()
+        if i >= warmup:
+            times.append(start.elapsed_time(stop))
+        for s in slots:
+            engine.release(s)
+    ms = sorted(times)[len(times) // 2]
+    out["prefill"] = {"tokens": PROMPTS_PER_STEP * PROMPT, "ms": round(ms, 3), "tok_s": round(PROMPTS_PER_STEP * PROMPT / ms * 1e3)}
+    # ---- decode steps
+    for batch in decode_batches:
+        slots = [engine.new_sequence() for _ in range(batch)]
+        first = torch.empty(batch, dtype=torch.int32, device="cuda")
+        for at in range(0, batch, 8):
+            part = slots[at:at + 8]
+            logits = engine.step(part, prompts(len(part)))
+            ops.sample_rows(logits.contiguous(), None, None, first[at:at + len(part)])
+        tokens = first
+        for _ in range(warmup):
+            tokens = engine.pick_on_device(engine.step_on_device(slots, tokens))
+        torch.cuda.synchronize()
+        start, stop = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        before = ops.launches()
+        start.record()
+        for _ in range(steps):
+            tokens = engine.pick_on_device(engine.step_on_device(slots, tokens))
+        stop.record()
+        torch.cuda.synchronize()
+        engine.check()
+        ms = start.elapsed_time(stop) / steps
+        out[f"decode_batch{batch}"] = {"ms": round(ms, 4), "tok_s": round(batch * 1e3 / ms, 1),
+                                       "launches_per_step": (ops.launches() - before) // steps,
+                                       "weights_gbs": round(out["weight_bytes"] / ms / 1e6, 1)}
+        if batch == decode_batches[0]:
+            # every kernel of one decode step, run directly
+            recording, engine.record_steps = engine.record_steps, False
+            engine.step(slots, [[1]] * batch)
+            ops.timing_start()
+            engine.step(slots, [[1]] * batch)
+            out["decode_kernels_ms"] = {k: [n, round(v, 4)] for k, (n, v) in sorted(ops.timing_report().items())}
+            engine.record_steps = recording
+        for s in slots:
+            engine.release(s)
+    # ---- every kernel of one step of prompts
+    slots = [engine.new_sequence() for _ in range(PROMPTS_PER_STEP)]
+    ops.timing_start()
+    engine.step(slots, prompts(PROMPTS_PER_STEP))
+    out["prefill_kernels_ms"] = {k: [n, round(v, 4)] for k, (n, v) in sorted(ops.timing_report().items())}
+    for s in slots:
+        engine.release(s)
+    return out
+
+
+def compare_designs(sizes=("w2048", "w4096"), steps: int = 8, warmup: int = 3) -> dict[str, Any]:
+    import fieldrun_b200 as fr
+    result: dict[str, Any] = {"prompt_tokens": PROMPT, "prompts_per_step": PROMPTS_PER_STEP, "dtype": "bf16",
+                              "data": "synthetic tokens, random weights", "sizes": {}}
+    for name in sizes:
+        size = SIZES[name]
+        entry: dict[str, Any] = {"size": size}
+        for design, config in (("bamasun", bamasun_config(**size)), ("minimax_m2", minimax_config(**size))):
+            began = time.time()
+            lm = fr.random_model(config, fr.RandomInit(seed=1, matrix_std=0.02, norm_std=0.1, bias_std=0.02), dtype="bfloat16",
+                                 max_tokens=64 * (PROMPT + 256), num_slots=72, max_batch=64)
+            entry[design] = _measure(lm, size["vocab"], steps, max(warmup, 3))
+            entry[design]["build_s"] = round(time.time() - began, 1)
+            del lm
+            torch.cuda.empty_cache()
+        result["sizes"][name] = entry
+    return result

@@ -633,11 +633,33 @@ __global__ void unary_unit_kernel(const float* __restrict__ in, OutT* __restrict
     out[i] = from_f32<OutT>(r);
 }
 
+// The same, four elements a thread (total a multiple of four, both arrays on 16 bytes).
+template <typename OutT>
+__global__ void unary_unit_vec_kernel(const float* __restrict__ in, OutT* __restrict__ out, int kind, size_t groups) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= groups) return;
+    float4 z = *reinterpret_cast<const float4*>(in + 4 * i);
+    float* e = reinterpret_cast<float*>(&z);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+        const float v = e[j];
+        if (kind == 0) { const float m = fmaxf(v, 0.f); e[j] = m * m; }
+        else if (kind == 1) e[j] = 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+        else if (kind == 2) e[j] = v / (1.0f + expf(-v));
+        else e[j] = fmaxf(v, 0.f);
+    }
+    store4<OutT>(out + 4 * i, z);
+}
+
 FRB_API int frb_unary_unit(const float* in, void* out, int out_dtype, long long total, int kind, cudaStream_t stream) {
     if (total == 0) return 0;
     FRB_CHECK_ARG(kind >= 0 && kind <= 3, "unary_unit: activation %d is none of 0..3", kind);
+    const bool by_four = total % 4 == 0 && ((uintptr_t)in & 15) == 0 && ((uintptr_t)out & 15) == 0;
     FRB_DISPATCH_DTYPE(out_dtype, OutT, {
-        unary_unit_kernel<OutT><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(in, (OutT*)out, kind, (size_t)total);
+        if (by_four)
+            unary_unit_vec_kernel<OutT><<<(unsigned)((total / 4 + 255) / 256), 256, 0, stream>>>(in, (OutT*)out, kind, (size_t)(total / 4));
+        else
+            unary_unit_kernel<OutT><<<(unsigned)((total + 255) / 256), 256, 0, stream>>>(in, (OutT*)out, kind, (size_t)total);
     });
     FRB_RETURN_LAUNCH("unary_unit");
 }

@@ -15,9 +15,10 @@
 //
 // One kernel serves a prompt's tokens and a single token.  A block takes a (work item, head): the item is a sequence's
 // new tokens, or a segment of them.  A warp owns a run of key channels, a lane VP value columns (v = lane + 32 j), and
-// each thread keeps its 64 elements of the state in registers; tokens are taken sixteen at a time: their q, k, alpha
-// and v are prepared in shared memory by the whole block, the sixteen steps then run without a barrier (three
-// broadcast loads for 2 VP multiply-adds on each channel), and the block finishes their outputs together.
+// each thread keeps its 64 elements of the state in registers; tokens are taken eight at a time: their q, k, alpha
+// and v are prepared in shared memory by the whole block, the eight steps then run without a barrier (one
+// broadcast load of 16 bytes, a channel's q, k and alpha, for 2 VP multiply-adds), and the block finishes their
+// outputs together.
 //
 // A long prompt alone would leave most of the device idle (one block per sequence and head, its tokens in order), so
 // its tokens are cut into segments that run side by side, in three launches:
@@ -29,7 +30,7 @@
 // The sums are those of the plain recurrence in another order, all in float32.
 #include "common.cuh"
 
-#define GLA_TOKENS 16        // tokens prepared together
+#define GLA_TOKENS 8         // tokens prepared together (few, so that two blocks share an SM: one prepares while one multiplies)
 #define GLA_STATE_REGS 64    // elements of the state that one thread keeps
 
 enum { GLA_WHOLE = 0, GLA_LOCAL = 1, GLA_OUTPUT = 3 };
@@ -55,6 +56,7 @@ struct GlaParams {
     int heads, dim, vdim, rank;
     int mode;
     int vpad, dpad, parts, dchunk;   // a block is `parts` warps; a warp keeps dchunk channels; dpad = parts * dchunk
+    int a2_shared;                   // the head's rows of A2 fit into shared memory beside the rest
 };
 
 __device__ __forceinline__ float log_sigmoid(float z) {
@@ -62,22 +64,23 @@ __device__ __forceinline__ float log_sigmoid(float z) {
     return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
-template <typename WT, typename OutT, int VP>
-__global__ void gla_scan_kernel(GlaParams p) {
+// LOCAL: launch 1 of a segmented prompt, which needs neither queries nor outputs.
+template <typename WT, typename OutT, int VP, bool LOCAL>
+__global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
     constexpr int DC = GLA_STATE_REGS / VP;
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     after_previous_kernel();
     const int item = blockIdx.x, h = blockIdx.y;
     const int dim = p.dim, vdim = p.vdim, rank = p.rank;
     const int vpad = p.vpad, dpad = p.dpad, parts = p.parts, dchunk = p.dchunk;
     const int nthreads = blockDim.x;
-    float* s_q = sm;                                   // [GLA_TOKENS][dpad]
-    float* s_k = s_q + GLA_TOKENS * dpad;
-    float* s_a = s_k + GLA_TOKENS * dpad;
-    float* s_v = s_a + GLA_TOKENS * dpad;              // [GLA_TOKENS][vpad]
+    float4* s_qka = reinterpret_cast<float4*>(sm);     // [GLA_TOKENS][dpad]: (q, k, alpha, log alpha) of a channel
+    float* s_v = sm + 4 * GLA_TOKENS * dpad;           // [GLA_TOKENS][vpad]
     float* s_a1 = s_v + GLA_TOKENS * vpad;             // [GLA_TOKENS][rank]
     float* s_o = s_a1 + GLA_TOKENS * rank;             // [GLA_TOKENS][parts][vpad]
     float* s_logsum = s_o + GLA_TOKENS * parts * vpad; // [dpad]
+    float* s_a2 = s_logsum + dpad;                     // [dim][rank + 1] if a2_shared: row d is read by thread d, so the
+                                                       // odd stride keeps a warp's loads on 32 banks
 
     const int b = p.seg_seq ? p.seg_seq[item] : item;
     const int row0 = p.cu_q_len[b], n_all = p.cu_q_len[b + 1] - row0;
@@ -101,11 +104,16 @@ __global__ void gla_scan_kernel(GlaParams p) {
         }
     for (int i = threadIdx.x; i < dpad; i += nthreads) s_logsum[i] = 0.f;
     // the padding of the rows stays zero: q = k = alpha = 0 there keeps a padded element of the state at zero
-    for (int i = threadIdx.x; i < GLA_TOKENS * dpad; i += nthreads) { s_q[i] = 0.f; s_k[i] = 0.f; s_a[i] = 0.f; }
+    for (int i = threadIdx.x; i < GLA_TOKENS * dpad; i += nthreads) s_qka[i] = make_float4(0.f, 0.f, 0.f, 0.f);
     for (int i = threadIdx.x; i < GLA_TOKENS * vpad; i += nthreads) s_v[i] = 0.f;
 
     const WT* a2 = (const WT*)p.a2 + (size_t)h * dim * rank;
     const float* a2_bias = p.a2_bias + h * dim;
+    if (p.a2_shared)
+        for (int i = threadIdx.x; i < dim * rank; i += nthreads) {
+            const int d = i / rank, r = i - d * rank;
+            s_a2[d * (rank + 1) + r] = to_f32<WT>(a2[i]);
+        }
 
     for (int t0 = t_begin; t0 < t_end; t0 += GLA_TOKENS) {
         const int count = min(GLA_TOKENS, t_end - t0);
@@ -119,57 +127,52 @@ __global__ void gla_scan_kernel(GlaParams p) {
             const int t = i / vdim, c = i - t * vdim;
             s_v[t * vpad + c] = rows[(size_t)t * p.P + p.off_v + h * vdim + c];
         }
-        for (int i = threadIdx.x; i < count * dim; i += nthreads) {
-            const int t = i / dim, d = i - t * dim;
-            s_q[t * dpad + d] = rows[(size_t)t * p.P + p.off_q + h * dim + d] * p.q_scale;
-            s_k[t * dpad + d] = rows[(size_t)t * p.P + p.off_k + h * dim + d];
-        }
         __syncthreads();
         for (int i = threadIdx.x; i < count * dim; i += nthreads) {
             const int t = i / dim, d = i - t * dim;
+            const float qv = LOCAL ? 0.f : rows[(size_t)t * p.P + p.off_q + h * dim + d] * p.q_scale;
+            const float kv = rows[(size_t)t * p.P + p.off_k + h * dim + d];
             float z = a2_bias[d];
-            const WT* w = a2 + (size_t)d * rank;
             const float* a1 = s_a1 + t * rank;
-            for (int r = 0; r < rank; ++r) z += to_f32<WT>(w[r]) * a1[r];
-            s_a[t * dpad + d] = log_sigmoid(z) * p.inv_tau;          // the decay's logarithm, for now
+            if (p.a2_shared) {
+                const float* w = s_a2 + d * (rank + 1);
+                for (int r = 0; r < rank; ++r) z += w[r] * a1[r];
+            } else {
+                const WT* w = a2 + (size_t)d * rank;
+                for (int r = 0; r < rank; ++r) z += to_f32<WT>(w[r]) * a1[r];
+            }
+            const float la = log_sigmoid(z) * p.inv_tau;
+            s_qka[t * dpad + d] = make_float4(qv, kv, expf(la), la);
         }
         __syncthreads();
-        if (p.mode == GLA_LOCAL)
+        if (LOCAL)
             for (int d = threadIdx.x; d < dim; d += nthreads) {
                 float sum = s_logsum[d];
-                for (int t = 0; t < count; ++t) sum += s_a[t * dpad + d];
+                for (int t = 0; t < count; ++t) sum += s_qka[t * dpad + d].w;
                 s_logsum[d] = sum;
             }
-        __syncthreads();
-        for (int i = threadIdx.x; i < count * dim; i += nthreads) {
-            const int t = i / dim, d = i - t * dim;
-            s_a[t * dpad + d] = expf(s_a[t * dpad + d]);
-        }
-        __syncthreads();
         for (int t = 0; t < count; ++t) {
-            const float* q = s_q + t * dpad + d0;
-            const float* k = s_k + t * dpad + d0;
-            const float* a = s_a + t * dpad + d0;
+            const float4* qka = s_qka + t * dpad + d0;
             float vt[VP], o[VP];
 #pragma unroll
             for (int j = 0; j < VP; ++j) { vt[j] = s_v[t * vpad + lane + 32 * j]; o[j] = 0.f; }
 #pragma unroll
             for (int i = 0; i < DC; ++i) {
                 if (i < dchunk) {
-                    const float ai = a[i], ki = k[i], qi = q[i];
+                    const float4 c = qka[i];
 #pragma unroll
                     for (int j = 0; j < VP; ++j) {
-                        S[i][j] = ai * S[i][j] + ki * vt[j];
-                        o[j] += qi * S[i][j];
+                        S[i][j] = c.z * S[i][j] + c.y * vt[j];
+                        if (!LOCAL) o[j] += c.x * S[i][j];
                     }
                 }
             }
-            if (p.mode != GLA_LOCAL) {
+            if (!LOCAL) {
 #pragma unroll
                 for (int j = 0; j < VP; ++j) s_o[(t * parts + part) * vpad + lane + 32 * j] = o[j];
             }
         }
-        if (p.mode == GLA_LOCAL) continue;
+        if (LOCAL) continue;
         __syncthreads();
         // a warp finishes a token: the parts of o added in order, the head's root mean square, weight and gate
         for (int t = part; t < count; t += parts) {
@@ -200,7 +203,7 @@ __global__ void gla_scan_kernel(GlaParams p) {
             const int d = d0 + i, v = lane + 32 * j;
             if (i < dchunk && d < dim && v < vdim) s_out[(size_t)d * vdim + v] = S[i][j];
         }
-    if (p.mode == GLA_LOCAL) {
+    if (LOCAL) {
         __syncthreads();
         for (int d = threadIdx.x; d < dim; d += nthreads) p.seg_decay[((size_t)item * p.heads + h) * dim + d] = expf(s_logsum[d]);
     }
@@ -254,11 +257,14 @@ FRB_API int frb_gla_scan(const float* proj, int P, int off_q, int off_k, int off
     const int most = GLA_STATE_REGS / vp;                 // channels a warp can keep
     int parts = (dim + most - 1) / most;
     if (parts < 8) parts = dim < 8 ? dim : 8;             // eight warps where the sizes allow
-    FRB_CHECK_ARG(parts <= 32, "gla: a state of %d x %d per head needs more than 1024 threads", dim, vdim);
+    FRB_CHECK_ARG(parts <= 16, "gla: a state of %d x %d per head is more than 512 threads keep in registers (32,768 elements)", dim, vdim);
     p.parts = parts;
     p.dchunk = (dim + parts - 1) / parts;
     p.dpad = p.parts * p.dchunk;
-    const size_t smem = ((size_t)GLA_TOKENS * (3 * p.dpad + p.vpad + rank) + (size_t)GLA_TOKENS * parts * p.vpad + p.dpad) * sizeof(float);
+    size_t smem = ((size_t)GLA_TOKENS * (4 * p.dpad + p.vpad + rank) + (size_t)GLA_TOKENS * parts * p.vpad + p.dpad) * sizeof(float);
+    const size_t a2_bytes = (size_t)dim * (rank + 1) * sizeof(float);
+    p.a2_shared = smem + a2_bytes <= 200 * 1024;          // (the registers of the state leave an SM one block of 256 threads anyway)
+    if (p.a2_shared) smem += a2_bytes;
     FRB_CHECK_ARG(smem <= 200 * 1024, "gla: %d x %d per head with rank %d needs more than 200 KB of shared memory", dim, vdim, rank);
     const bool segmented = seg_seq != nullptr;
     FRB_CHECK_ARG(!segmented || (seg_begin && seg_end && seq_seg0 && seg_scratch && num_items > 0), "gla: segment tables are incomplete");
@@ -271,14 +277,16 @@ FRB_API int frb_gla_scan(const float* proj, int P, int off_q, int off_k, int off
     const dim3 grid(segmented ? num_items : num_seqs, heads), block(32 * parts);
 #define FRB_GLA_LAUNCH(VP)                                                                                            \
     do {                                                                                                              \
-        auto kernel = gla_scan_kernel<WT, OutT, VP>;                                                                  \
+        auto kernel = gla_scan_kernel<WT, OutT, VP, false>;                                                           \
+        auto local = gla_scan_kernel<WT, OutT, VP, true>;                                                             \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        if (smem > 48 * 1024) cudaFuncSetAttribute(local, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         if (!segmented) {                                                                                             \
             p.mode = GLA_WHOLE;                                                                                       \
             launch_dependent(kernel, grid, block, smem, stream, p);                                                   \
         } else {                                                                                                      \
             p.mode = GLA_LOCAL;                                                                                       \
-            kernel<<<grid, block, smem, stream>>>(p);                                                                 \
+            local<<<grid, block, smem, stream>>>(p);                                                                  \
             gla_combine_kernel<<<dim3(num_seqs, heads, (dim * vdim + 255) / 256), 256, 0, stream>>>(                  \
                 p.seg_local, p.seg_decay, seg_first, state, seq_slot, seq_start, cu_q_len, seq_seg0, heads, dim, vdim); \
             p.mode = GLA_OUTPUT;                                                                                      \

@@ -29,6 +29,7 @@ import torch
 from .csrc import ops
 
 HIDDEN, WIDTH, HEADS, KV_HEADS, HEAD_DIM = 3072, 1536, 48, 8, 128
+DEV = "cuda"
 
 
 def _time(launch, launches: int, warmup: int = 3) -> float:
@@ -310,7 +311,52 @@ def step_timeline(launches: int, batch: int = 8) -> dict:
             "middle_layer": rows}
 
 
+def linear_attention(kind: str, launches: int) -> dict:
+    """The gated linear attention scan alone, 16 heads of 128 x 128 with a decay of rank 32: ``prefill`` four prompts of
+    2,048 tokens in segments of 128 (three launches a call), ``prefill_whole`` the same without segments, ``decode`` 64
+    sequences of one token.  FLOPs are those of the recurrence: four per state element and token."""
+    heads, dim, vdim, rank = 16, 128, 128, 32
+    if kind == "decode":
+        lengths = [1] * 64
+    else:
+        lengths = [2048] * 4
+    tokens = sum(lengths)
+    P = 2 * heads * dim + 2 * heads * vdim + rank
+    proj = torch.randn(tokens, P, device=DEV) * 0.5
+    a2 = (torch.randn(heads * dim, rank, device=DEV) * 0.3).to(torch.bfloat16)
+    bias = torch.randn(heads * dim, device=DEV) + 2.0
+    norm = torch.ones(vdim, device=DEV)
+    state = torch.zeros(len(lengths), 2, heads, dim, vdim, device=DEV)
+    out = torch.empty(tokens, heads * vdim, dtype=torch.bfloat16, device=DEV)
+    slots = torch.arange(len(lengths), dtype=torch.int32, device=DEV)
+    starts = torch.zeros(len(lengths), dtype=torch.int32, device=DEV)
+    cu = torch.tensor([0] + list(np.cumsum(lengths)), dtype=torch.int32, device=DEV)
+    segments = scratch = None
+    if kind == "prefill":
+        size, seqs, lo, hi, first = 128, [], [], [], [0]
+        for b, n in enumerate(lengths):
+            for t in range(0, n, size):
+                seqs.append(b), lo.append(t), hi.append(min(t + size, n))
+            first.append(len(seqs))
+        segments = tuple(torch.tensor(x, dtype=torch.int32, device=DEV) for x in (seqs, lo, hi, first))
+        scratch = torch.empty(ops.gla_scratch_floats(len(seqs), heads, dim, vdim), device=DEV)
+    offsets = (0, heads * dim, 2 * heads * dim, 2 * heads * dim + heads * vdim, 2 * heads * dim + 2 * heads * vdim)
+
+    def launch():
+        ops.gla_scan(proj, offsets, a2, bias, norm, state, slots, starts, cu, out, heads=heads, dim=dim, vdim=vdim, tau=16.0,
+                     q_scale=dim ** -0.5, eps=1e-6, segments=segments, scratch=scratch)
+
+    ms = _time(launch, launches)
+    flops = 4.0 * tokens * heads * dim * vdim
+    moved = proj.numel() * 4 + out.numel() * 2 + (2 * state[:, 0].numel() * 4 if kind == "decode" else 0)
+    return {"case": f"linear_attention_{kind}", "tokens": tokens, "ms": round(ms, 4), "tflops_float32": round(flops / ms / 1e9, 2),
+            "gbs": round(moved / ms / 1e6, 1)}
+
+
 CASES = {
+    "linear_attention_prefill": lambda n: linear_attention("prefill", n),
+    "linear_attention_prefill_whole": lambda n: linear_attention("prefill_whole", n),
+    "linear_attention_decode": lambda n: linear_attention("decode", n),
     "experts_tc": lambda n: experts("tc", n),
     "experts_tc_large": lambda n: experts("tc_large", n),
     "experts_stream": lambda n: experts("stream", n),
