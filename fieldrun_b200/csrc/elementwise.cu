@@ -6,22 +6,7 @@
 // rotate-half pairs (j, j+half) by pos*inv[j] (src/minimax.rs:69-84, partial form
 // src/qwen35moe.rs:121-138), K cached after norm and rotary, V as projected (src/minimax.rs:262-268).
 // All statistics and the residual sum are float32.
-#include <stdarg.h>
-
 #include "common.cuh"
-
-static thread_local char g_error[1024] = "";
-
-void frb_set_error(const char* fmt, ...) {
-    va_list args;
-    va_start(args, fmt);
-    vsnprintf(g_error, sizeof(g_error), fmt, args);
-    va_end(args);
-}
-
-FRB_API const char* frb_last_error() { return g_error; }
-
-FRB_API int frb_abi_version() { return 3; }
 
 // ----------------------------------------------------------------------------- embedding rows
 

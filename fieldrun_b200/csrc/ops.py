@@ -13,8 +13,8 @@ import torch
 
 from . import build as _build
 
-_LIB: ctypes.CDLL | None = None
-_LIB_PATH: str | None = None
+_LIBS: dict[str, ctypes.CDLL] = {}
+_LIB_PATHS: dict[str, str] = {}
 
 _P, _I, _F, _L = ctypes.c_void_p, ctypes.c_int, ctypes.c_float, ctypes.c_longlong
 
@@ -57,33 +57,61 @@ class KernelError(RuntimeError):
     pass
 
 
-def library() -> ctypes.CDLL:
-    """The compiled kernels; built at the first call."""
-    global _LIB, _LIB_PATH
-    if _LIB is None:
-        path = _build.build()
-        lib = ctypes.CDLL(path)
+# which library of kernels (a group of build.GROUPS) holds which entry point
+_ENTRY_GROUPS = {
+    "common": ("frb_embed_rows", "frb_rmsnorm", "frb_qkv_prepare", "frb_add_rows", "frb_attention_generic", "frb_layernorm",
+               "frb_unary_unit", "frb_softcap", "frb_gated_unit", "frb_sample_rows", "frb_argmax_rows", "frb_sample_floor"),
+    "attention": ("frb_attention_decode_mma", "frb_attention_prefill_mma", "frb_attention_decode_tma", "frb_attention_prefill_tc"),
+    "streams": ("frb_weight_stream", "frb_expert_gemm_mma"),
+    "experts": ("frb_router_topk", "frb_expert_plan", "frb_expert_combine", "frb_expert_gemm_generic", "frb_route_plan_small",
+                "frb_router_small", "frb_router_logits", "frb_expert_gemm_tc", "frb_gather_rows_bf16"),
+    "recurrent": ("frb_gla_scan",),
+    "extras": ("frb_wait_probe",),
+}
+_GROUP_OF = {entry: group for group, entries in _ENTRY_GROUPS.items() for entry in entries}
+
+
+def prepare(groups) -> None:
+    """Build (what is missing, all at once) and load the libraries of ``groups``.  A model does this for the groups of
+    its parts before its first step; an entry point of a group that nobody prepared is built when it is first called."""
+    wanted = [g for g in dict.fromkeys(groups) if g not in _LIBS]
+    if not wanted:
+        return
+    paths = _build.build(wanted)
+    for group in wanted:
+        lib = ctypes.CDLL(paths[group])
         lib.frb_last_error.restype = ctypes.c_char_p
         lib.frb_last_error.argtypes = []
-        for name, spec in _SIGNATURES.items():
+        for name in _ENTRY_GROUPS.get(group, ()):
             fn = getattr(lib, name)
             fn.restype = _I
-            fn.argtypes = [_CTYPE[c] for c in spec] + [_P]
-        _LIB, _LIB_PATH = lib, path
-    return _LIB
+            fn.argtypes = [_CTYPE[c] for c in _SIGNATURES[name]] + [_P]
+        _LIBS[group], _LIB_PATHS[group] = lib, paths[group]
 
 
-def library_file() -> str:
-    library()
-    assert _LIB_PATH is not None
-    return _LIB_PATH
+def library(group: str = "common") -> ctypes.CDLL:
+    """The compiled kernels of one group; built at the first call."""
+    if group not in _LIBS:
+        prepare([group])
+    return _LIBS[group]
 
 
-def register(name: str, spec: str) -> None:
-    """Declare one more entry point of the library (used by kernels that live in files of their own)."""
+def library_file(group: str = "common") -> str:
+    library(group)
+    return _LIB_PATHS[group]
+
+
+def library_files() -> dict[str, str]:
+    """group -> file of every library loaded so far."""
+    return dict(_LIB_PATHS)
+
+
+def register(name: str, spec: str, group: str = "extras") -> None:
+    """Declare one more entry point (used by kernels that live in files of their own)."""
     _SIGNATURES[name] = spec
-    if _LIB is not None:
-        fn = getattr(_LIB, name)
+    _GROUP_OF[name] = group
+    if group in _LIBS:
+        fn = getattr(_LIBS[group], name)
         fn.restype = _I
         fn.argtypes = [_CTYPE[c] for c in spec] + [_P]
 
@@ -177,7 +205,7 @@ class timed:
 
 def _call(name: str, *args) -> None:
     global _LAUNCHES
-    lib = library()
+    lib = library(_GROUP_OF[name])
     if _TIMINGS is not None:
         with timed(name[4:]):
             status = getattr(lib, name)(*args, _stream())

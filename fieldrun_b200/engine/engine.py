@@ -97,7 +97,7 @@ class Engine:
             raise RuntimeError("fieldrun_b200 needs a CUDA device (sm_100a); there is no CPU path")
         self.model = model
         self.device = torch.device(device)
-        ops.library()                                   # build or load the kernels now, and fail here if that fails
+        ops.prepare(model.kernel_groups())              # build or load the model's kernels now, and fail here if that fails
         self.cache: SequenceCache = model.new_cache(max_tokens, num_slots, self.device)
         self.workspace = Workspace(self.device)
         self.vocab_size = model.plan.vocab_size

@@ -82,6 +82,15 @@ class DecoderModel:
             self.head.load(source)
         self.loaded = True
 
+    def kernel_groups(self) -> list[str]:
+        """The libraries of kernels that the model's parts launch from, each once."""
+        groups: list[str] = []
+        for part in self.all_parts():
+            for group in part.kernel_groups:
+                if group not in groups:
+                    groups.append(group)
+        return groups
+
     @property
     def replayable(self) -> bool:
         """Whether a step of this model can be recorded once and run again (see ``Part.replayable``)."""

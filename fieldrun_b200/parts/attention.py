@@ -36,6 +36,7 @@ TC_ATTENTION_MIN_QUERIES = 64       # a step whose longest run of new tokens is 
 
 class GQAAttention(Mixer):
     replayable = True
+    kernel_groups = ("common", "streams", "attention")
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)

@@ -43,6 +43,9 @@ class Part:
     that leaves it False is always run directly."""
 
     replayable: bool = False
+    # the libraries of kernels (groups of ``csrc/build.py``) that the part launches from; a model compiles and loads
+    # the groups of its parts, and no others, before its first step
+    kernel_groups: tuple[str, ...] = ("common", "streams")
 
     def __init__(self, spec: PartSpec, dtype: torch.dtype):
         self.spec = spec

@@ -31,6 +31,8 @@ TENSOR_CORE_ROWS_PER_EXPERT = {"decode": 4.0, "prompt": 1.0}
 
 
 class RoutedExperts(FeedForward):
+    kernel_groups = ("common", "streams", "experts")
+
     wants_float32_input = True          # the router reads the normed rows before they are rounded
     replayable = True
 

@@ -31,6 +31,7 @@ SEGMENT_TOKENS = 128        # a long prompt's tokens run in segments of this man
 
 class GatedLinearAttention(Mixer):
     replayable = True
+    kernel_groups = ("common", "streams", "recurrent")
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)

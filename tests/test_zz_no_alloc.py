@@ -17,7 +17,7 @@ DEV = "cuda"
 
 def _symbol():
     from fieldrun_b200.csrc import ops
-    lib = ctypes.CDLL(ops.library_file())
+    lib = ctypes.CDLL(ops.library_file("extras"))
     fn = lib.frb_attention_decode_noalloc
     fn.restype = ctypes.c_int
     p, i, f = ctypes.c_void_p, ctypes.c_int, ctypes.c_float
