@@ -57,6 +57,7 @@ struct GlaParams {
     int mode;
     int vpad, dpad, parts, dchunk;   // a block is `parts` warps; a warp keeps dchunk channels; dpad = parts * dchunk
     int a2_shared;                   // the head's rows of A2 fit into shared memory beside the rest
+    int a2_stride;                   // floats from one of those rows to the next
 };
 
 __device__ __forceinline__ float log_sigmoid(float z) {
@@ -79,8 +80,10 @@ __global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
     float* s_a1 = s_v + GLA_TOKENS * vpad;             // [GLA_TOKENS][rank]
     float* s_o = s_a1 + GLA_TOKENS * rank;             // [GLA_TOKENS][parts][vpad]
     float* s_logsum = s_o + GLA_TOKENS * parts * vpad; // [dpad]
-    float* s_a2 = s_logsum + dpad;                     // [dim][rank + 1] if a2_shared: row d is read by thread d, so the
-                                                       // odd stride keeps a warp's loads on 32 banks
+    float* s_a2 = s_logsum + ((dpad + 3) & ~3);                   // [dim][a2_stride] if a2_shared: row d is read by thread d; the stride
+                                                       // (rank + 1, or rank + 4 where rows are read 16 bytes at a time) keeps
+                                                       // a warp's loads on all banks
+    const int a2_stride = p.a2_stride;
 
     const int b = p.seg_seq ? p.seg_seq[item] : item;
     const int row0 = p.cu_q_len[b], n_all = p.cu_q_len[b + 1] - row0;
@@ -112,7 +115,7 @@ __global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
     if (p.a2_shared)
         for (int i = threadIdx.x; i < dim * rank; i += nthreads) {
             const int d = i / rank, r = i - d * rank;
-            s_a2[d * (rank + 1) + r] = to_f32<WT>(a2[i]);
+            s_a2[d * a2_stride + r] = to_f32<WT>(a2[i]);
         }
 
     for (int t0 = t_begin; t0 < t_end; t0 += GLA_TOKENS) {
@@ -134,8 +137,18 @@ __global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
             const float kv = rows[(size_t)t * p.P + p.off_k + h * dim + d];
             float z = a2_bias[d];
             const float* a1 = s_a1 + t * rank;
-            if (p.a2_shared) {
-                const float* w = s_a2 + d * (rank + 1);
+            if (p.a2_shared && (rank & 3) == 0) {
+                const float4* w = reinterpret_cast<const float4*>(s_a2 + d * a2_stride);
+                const float4* x = reinterpret_cast<const float4*>(a1);
+                for (int r = 0; r < rank / 4; ++r) {
+                    const float4 wv = w[r], xv = x[r];
+                    z += wv.x * xv.x;
+                    z += wv.y * xv.y;
+                    z += wv.z * xv.z;
+                    z += wv.w * xv.w;
+                }
+            } else if (p.a2_shared) {
+                const float* w = s_a2 + d * a2_stride;
                 for (int r = 0; r < rank; ++r) z += w[r] * a1[r];
             } else {
                 const WT* w = a2 + (size_t)d * rank;
@@ -261,8 +274,9 @@ FRB_API int frb_gla_scan(const float* proj, int P, int off_q, int off_k, int off
     p.parts = parts;
     p.dchunk = (dim + parts - 1) / parts;
     p.dpad = p.parts * p.dchunk;
-    size_t smem = ((size_t)GLA_TOKENS * (4 * p.dpad + p.vpad + rank) + (size_t)GLA_TOKENS * parts * p.vpad + p.dpad) * sizeof(float);
-    const size_t a2_bytes = (size_t)dim * (rank + 1) * sizeof(float);
+    size_t smem = ((size_t)GLA_TOKENS * (4 * p.dpad + p.vpad + rank) + (size_t)GLA_TOKENS * parts * p.vpad + ((p.dpad + 3) & ~3)) * sizeof(float);
+    p.a2_stride = rank % 4 == 0 ? rank + 4 : rank + 1;
+    const size_t a2_bytes = (size_t)dim * p.a2_stride * sizeof(float);
     p.a2_shared = smem + a2_bytes <= 200 * 1024;          // (the registers of the state leave an SM one block of 256 threads anyway)
     if (p.a2_shared) smem += a2_bytes;
     FRB_CHECK_ARG(smem <= 200 * 1024, "gla: %d x %d per head with rank %d needs more than 200 KB of shared memory", dim, vdim, rank);
