@@ -1,5 +1,10 @@
 """The Bamasun design in the engine against the plain implementation of ``plain_bamasun``: each mechanism's kernel
 alone, then whole models through the step function, the cache, recorded decode steps and the entry point."""
+import json
+import os
+import subprocess
+import sys
+
 import numpy as np
 import pytest
 import torch
@@ -579,3 +584,48 @@ def test_greedy_generation_through_the_entry_point():
             ids.append(int(np.argmax(row)))
         assert tokens == ids[len(prompt):]
     assert lm.generate(prompts[0], 5) == got[0][:5]
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_a_trace_replayed_through_the_runner(tmp_path, dtype):
+    """bin/trace_run as a user drives it: a batch of three prompts of unequal lengths (one of a single token, one of
+    which nothing is wanted), decoded together while the shorter requests end, then another batch in the freed slots."""
+    name = "B"
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    vocab = ALL[name][0]["vocab"]
+    lengths = {"p": 1 + 6, "q": 80 + 20, "r": 130 + 9, "s": 65 + 12}
+    heads = {"p": 1, "q": 80, "r": 130, "s": 65}
+    ids = {k: request_tokens(name, n, 70 + i) for i, (k, n) in enumerate(lengths.items())}
+    steps, rows, step = [], {k: [] for k in ids}, 0
+    for batch in (["p", "q", "r"], ["s"]):
+        entries = []
+        at = 0
+        for k in batch:
+            want = [] if k == "q" else ([0] if heads[k] == 1 else [0, heads[k] // 2, heads[k] - 1])
+            entries.append({"id": k, "tokens": ids[k][:heads[k]], "want": want})
+            for w in want:
+                rows[k].append((step, at, w))
+                at += 1
+        steps.append({"step": step, "entries": entries, "end": []})
+        step += 1
+        for t in range(max(lengths[k] - heads[k] for k in batch)):
+            live = [k for k in batch if heads[k] + t < lengths[k]]
+            steps.append({"step": step, "entries": [{"id": k, "tokens": [ids[k][heads[k] + t]], "want": [0]} for k in live],
+                          "end": [k for k in live if heads[k] + t == lengths[k] - 1]})
+            for row, k in enumerate(live):
+                rows[k].append((step, row, heads[k] + t))
+            step += 1
+    text = "".join(json.dumps(x) + "\n" for x in steps)
+    proc = subprocess.run([sys.executable, os.path.join(root, "bin", "trace_run"), "--model", model_folder(name), "--dtype", dtype,
+                           "--out", str(tmp_path), "--max-tokens", "384"], input=text, capture_output=True, text=True, timeout=900)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    assert [line for line in proc.stdout.splitlines() if line.startswith("done ")] == [f"done {x['step']}" for x in steps]
+    out = {}
+    for x in steps:
+        wanted = sum(len(e["want"]) for e in x["entries"])
+        if wanted:
+            out[x["step"]] = np.fromfile(os.path.join(tmp_path, f"{x['step']}.f32"), dtype="<f4").reshape(wanted, vocab)
+    for i, (k, n) in enumerate(lengths.items()):
+        plain = plain_logits(name, n, 70 + i)
+        got = np.stack([out[s][row] for s, row, _ in rows[k]])
+        model_close(got, plain[[pos for _, _, pos in rows[k]]], dtype, f"request {k}")
