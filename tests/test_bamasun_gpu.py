@@ -532,18 +532,18 @@ def test_prompts_in_portions(name, dtype, portion):
 @pytest.mark.parametrize("name", ["A", "B", "C"])
 def test_unequal_requests_in_one_batch_then_decoded_together_over_reused_slots(name, dtype):
     lm = loaded(name, dtype)
-    for round_ in range(2):                 # the second round takes the slots, pages and states the first gave back
-        lengths = {"a": 1 + 30, "b": 70 + 30, "c": 200 + 30, "d": 64 + 12, "e": 129 + 5} if round_ == 0 else \
+    for turn in range(2):                 # the second turn takes the slots, pages and states the first gave back
+        lengths = {"a": 1 + 30, "b": 70 + 30, "c": 200 + 30, "d": 64 + 12, "e": 129 + 5} if turn == 0 else \
                   {"a": 90 + 25, "b": 3 + 25, "c": 64 + 25}
-        tails = {"a": 30, "b": 30, "c": 30, "d": 12, "e": 5} if round_ == 0 else {"a": 25, "b": 25, "c": 25}
-        requests = {k: request_tokens(name, n, 20 + round_ * 10 + i) for i, (k, n) in enumerate(lengths.items())}
+        tails = {"a": 30, "b": 30, "c": 30, "d": 12, "e": 5} if turn == 0 else {"a": 25, "b": 25, "c": 25}
+        requests = {k: request_tokens(name, n, 20 + turn * 10 + i) for i, (k, n) in enumerate(lengths.items())}
         steps = [[(k, 0, lengths[k] - tails[k]) for k in lengths]]
         for t in range(max(tails.values())):
             steps.append([(k, lengths[k] - tails[k] + t, lengths[k] - tails[k] + t + 1) for k in lengths if t < tails[k]])
         got = run_schedule(lm, requests, steps)
         for i, k in enumerate(lengths):
-            model_close(got[k], plain_logits(name, lengths[k], 20 + round_ * 10 + i), dtype,
-                        f"model {name}, round {round_}, request {k}")
+            model_close(got[k], plain_logits(name, lengths[k], 20 + turn * 10 + i), dtype,
+                        f"model {name}, turn {turn}, request {k}")
 
 
 @pytest.mark.parametrize("name", ["A", "C"])
