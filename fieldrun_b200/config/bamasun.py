@@ -15,11 +15,13 @@ The file names the design as ``"architecture": "Bamasun"`` and lists the layers 
     gla:        heads, dim, vdim, tau  (the rank of the decay's inner product is the shape of its tensor)
 
 Everything that can differ between two models of the design is read here; the constants that the design fixes
-(the slopes' exponent, the activations) live with the plan in ``models/bamasun.py``.  A key the design does not
-have is refused, so that a file of another design is not run as this one.
+(the slopes' exponent, the activations) live with the plan in ``models/bamasun.py``.  Inside a layer, the
+embedding and the norm a key the design does not have is refused, so that a file of another design (a window, a
+sink, a cap on the scores) is not run as this one; at the top level such a key is a warning.
 """
 from __future__ import annotations
 
+import sys
 from dataclasses import dataclass
 from typing import Any, Mapping, Optional
 
@@ -128,8 +130,16 @@ class BamasunConfig(ModelConfig):
 
     @classmethod
     def from_dict(cls, raw: Mapping[str, Any], where: str = "config.json") -> "BamasunConfig":
-        _only(raw, {"architecture", "architectures", "model_type", "vocab", "width", "embedding", "norm", "logit_softcap",
-                    "layers", "eos_token_id"}, where)
+        known = {"architecture", "architectures", "model_type", "vocab", "width", "embedding", "norm", "logit_softcap",
+                 "layers", "eos_token_id"}
+        extra = sorted(set(raw) - known)
+        if extra:
+            # beside the model's sizes a file may carry notes of its writer (a name, a seed); inside a layer,
+            # where every key is arithmetic, an unknown key is refused
+            print(f"{where}: warning: top-level keys this design does not have are ignored: {', '.join(extra)}", file=sys.stderr)
+        for name in ("embedding", "norm"):
+            if isinstance(raw.get(name), Mapping):
+                _only(raw[name], {"scale"} if name == "embedding" else {"eps"}, f"{where}: {name}")
         r = KeyReader(raw, where)
         listed = raw.get("layers")
         if not isinstance(listed, list) or not listed:

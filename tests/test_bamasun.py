@@ -42,11 +42,13 @@ def test_config_refusals():
         (("layers", 0, "type"), "conv", "'attention' and 'gla'"),
         (("layers", 0, "mlp", "kind"), "moe", "'dense'"),
         (("layers", 1, "mixer", "window"), 128, "does not have"),
-        (("rope_theta",), 10000.0, "does not have"),
+        (("norm", "kind"), "rms", "does not have"),
         (("layers", 0, "mixer", "tau"), 0.0, "tau"),
     ]:
         with pytest.raises(ConfigError, match=match):
             BamasunConfig.from_dict(changed(path, value))
+    # a note of the file's writer at the top level is no arithmetic: a warning, and the configuration reads as before
+    assert BamasunConfig.from_dict(dict(CONFIG_A, seed=7)) == BamasunConfig.from_dict(CONFIG_A)
     # a layer cannot read the keys of a layer that itself reads another's
     raw = changed(("layers", 4, "mixer"), dict(CONFIG_A["layers"][2]["mixer"], kv_from=2))
     with pytest.raises(ConfigError, match="of its own"):
