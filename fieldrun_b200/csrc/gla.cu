@@ -56,6 +56,9 @@ struct GlaParams {
     int heads, dim, vdim, rank;
     int mode;
     int vpad, dpad, parts, dchunk;   // a block is `parts` warps; a warp keeps dchunk channels; dpad = parts * dchunk
+    float* raw_out;                  // null, or [T, heads * vdim]: the value columns are cut into slices over blocks (a state
+                                     // too large for one block's registers); the blocks leave o as it is here and a
+                                     // second kernel norms and gates it
     int a2_shared;                   // the head's rows of A2 fit into shared memory beside the rest
     int a2_stride;                   // floats from one of those rows to the next
 };
@@ -66,7 +69,8 @@ __device__ __forceinline__ float log_sigmoid(float z) {
 }
 
 // LOCAL: launch 1 of a segmented prompt, which needs neither queries nor outputs.
-template <typename WT, typename OutT, int VP, bool LOCAL>
+// SLICED: the value columns are cut over blocks (blockIdx.z) and the outputs go to raw_out.
+template <typename WT, typename OutT, int VP, bool LOCAL, bool SLICED>
 __global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
     constexpr int DC = GLA_STATE_REGS / VP;
     extern __shared__ __align__(16) float sm[];
@@ -97,13 +101,14 @@ __global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
 
     const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
     const int d0 = part * dchunk;
+    const int v0 = SLICED ? blockIdx.z * vpad : 0, vcount = SLICED ? min(vpad, vdim - v0) : vdim;   // this block's value columns
     float S[DC][VP];
 #pragma unroll
     for (int i = 0; i < DC; ++i)
 #pragma unroll
         for (int j = 0; j < VP; ++j) {
             const int d = d0 + i, v = lane + 32 * j;
-            S[i][j] = (s_in && i < dchunk && d < dim && v < vdim) ? s_in[(size_t)d * vdim + v] : 0.f;
+            S[i][j] = (s_in && i < dchunk && d < dim && v < vcount) ? s_in[(size_t)d * vdim + v0 + v] : 0.f;
         }
     for (int i = threadIdx.x; i < dpad; i += nthreads) s_logsum[i] = 0.f;
     // the padding of the rows stays zero: q = k = alpha = 0 there keeps a padded element of the state at zero
@@ -126,9 +131,9 @@ __global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
             const int t = i / rank, r = i - t * rank;
             s_a1[i] = rows[(size_t)t * p.P + p.off_a + r];
         }
-        for (int i = threadIdx.x; i < count * vdim; i += nthreads) {
-            const int t = i / vdim, c = i - t * vdim;
-            s_v[t * vpad + c] = rows[(size_t)t * p.P + p.off_v + h * vdim + c];
+        for (int i = threadIdx.x; i < count * vcount; i += nthreads) {
+            const int t = i / vcount, c = i - t * vcount;
+            s_v[t * vpad + c] = rows[(size_t)t * p.P + p.off_v + h * vdim + v0 + c];
         }
         __syncthreads();
         for (int i = threadIdx.x; i < count * dim; i += nthreads) {
@@ -189,6 +194,15 @@ __global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
         __syncthreads();
         // a warp finishes a token: the parts of o added in order, the head's root mean square, weight and gate
         for (int t = part; t < count; t += parts) {
+            if (SLICED) {
+                float* raw = p.raw_out + ((size_t)(row0 + t0 + t) * p.heads + h) * vdim + v0;
+                for (int c = lane; c < vcount; c += 32) {
+                    float o = 0.f;
+                    for (int s = 0; s < parts; ++s) o += s_o[(t * parts + s) * vpad + c];
+                    raw[c] = o;
+                }
+                continue;
+            }
             float ss = 0.f;
             for (int c = lane; c < vdim; c += 32) {
                 float o = 0.f;
@@ -214,12 +228,48 @@ __global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
 #pragma unroll
         for (int j = 0; j < VP; ++j) {
             const int d = d0 + i, v = lane + 32 * j;
-            if (i < dchunk && d < dim && v < vdim) s_out[(size_t)d * vdim + v] = S[i][j];
+            if (i < dchunk && d < dim && v < vcount) s_out[(size_t)d * vdim + v0 + v] = S[i][j];
         }
     if (LOCAL) {
         __syncthreads();
         for (int d = threadIdx.x; d < dim; d += nthreads) p.seg_decay[((size_t)item * p.heads + h) * dim + d] = expf(s_logsum[d]);
     }
+}
+
+// For a state cut into slices of value columns: out = raw / rms(raw over the head) * weight * silu(gate).
+// grid (token, head), one warp.
+template <typename OutT>
+__global__ void gla_finish_kernel(const float* __restrict__ raw, const float* __restrict__ proj, const float* __restrict__ norm_w,
+                                  OutT* __restrict__ out, int P, int off_g, int heads, int vdim, float eps) {
+    const int t = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+    const float* o = raw + ((size_t)t * heads + h) * vdim;
+    float ss = 0.f;
+    for (int c = lane; c < vdim; c += 32) ss += o[c] * o[c];
+    ss = warp_sum(ss);
+    const float rinv = 1.0f / sqrtf(ss / (float)vdim + eps);
+    const float* g = proj + (size_t)t * P + off_g + h * vdim;
+    for (int c = lane; c < vdim; c += 32) {
+        const float gate = g[c];
+        out[((size_t)t * heads + h) * vdim + c] = from_f32<OutT>(o[c] * rinv * norm_w[c] * (gate / (1.0f + expf(-gate))));
+    }
+}
+
+// How the value columns of a head's state are cut over blocks: columns per lane (1, 2, 4, 8) and slices of 32 times
+// that many columns.  One slice wherever a block's registers hold the state (dim x vdim up to 32,768 with padding).
+static inline bool gla_shape(int dim, int vdim, int* vp_out, int* slices_out) {
+    int vp = (vdim + 31) / 32;
+    vp = vp <= 1 ? 1 : vp == 2 ? 2 : vp <= 4 ? 4 : 8;
+    while (vp > 1 && (dim + GLA_STATE_REGS / vp - 1) / (GLA_STATE_REGS / vp) > 16) vp /= 2;
+    if ((dim + GLA_STATE_REGS / vp - 1) / (GLA_STATE_REGS / vp) > 16) return false;
+    *vp_out = vp;
+    *slices_out = (vdim + 32 * vp - 1) / (32 * vp);
+    return true;
+}
+
+// The number of slices (1: no raw buffer is needed), or 0 for sizes that no launch takes.
+FRB_API int frb_gla_value_slices(int dim, int vdim) {
+    int vp = 0, slices = 0;
+    return dim >= 1 && vdim >= 1 && gla_shape(dim, vdim, &vp, &slices) ? slices : 0;
 }
 
 // Launch 2 of a segmented prompt.  grid (sequence, head, tiles of 256 state elements).
@@ -252,25 +302,26 @@ FRB_API int frb_gla_scan(const float* proj, int P, int off_q, int off_k, int off
                          const int* seq_slot, const int* seq_start, const int* cu_q_len, void* out, int out_dtype,
                          int num_seqs, int heads, int dim, int vdim, int rank, float tau, float q_scale, float eps,
                          const int* seg_seq, const int* seg_begin, const int* seg_end, const int* seq_seg0, int num_items,
-                         float* seg_scratch, cudaStream_t stream) {
+                         float* seg_scratch, float* raw_out, int num_tokens, cudaStream_t stream) {
     if (num_seqs == 0) return 0;
+    FRB_CHECK_ARG(weight_dtype == out_dtype, "gla: the decay's matrix and the outputs must have one type");
     FRB_CHECK_ARG(dim >= 1 && vdim >= 1 && rank >= 1 && heads >= 1 && heads <= 65535, "gla: %d heads of %d x %d, rank %d",
                   heads, dim, vdim, rank);
     FRB_CHECK_ARG(tau > 0.f, "gla: tau %f", (double)tau);
-    FRB_CHECK_ARG(vdim <= 256, "gla: a value head of %d (at most 256)", vdim);
+    int vp = 0, slices = 0;
+    FRB_CHECK_ARG(gla_shape(dim, vdim, &vp, &slices), "gla: %d key channels a head are more than a block's registers hold (1,024)", dim);
+    FRB_CHECK_ARG(slices == 1 || raw_out, "gla: a state of %d x %d per head is cut into %d slices and needs the raw buffer", dim, vdim, slices);
+    FRB_CHECK_ARG(slices <= 65535, "gla: %d slices", slices);
     GlaParams p;
     p.proj = proj; p.a2 = a2; p.a2_bias = a2_bias; p.norm_w = norm_w; p.state = state; p.seq_slot = seq_slot;
     p.seq_start = seq_start; p.cu_q_len = cu_q_len; p.out = out; p.inv_tau = 1.0f / tau; p.q_scale = q_scale; p.eps = eps;
     p.P = P; p.off_q = off_q; p.off_k = off_k; p.off_v = off_v; p.off_g = off_g; p.off_a = off_a;
     p.heads = heads; p.dim = dim; p.vdim = vdim; p.rank = rank;
-    p.vpad = (vdim + 31) / 32 * 32;
-    int vp = p.vpad / 32;                                 // columns per lane: 1, 2, 4 or 8
-    if (vp == 3) vp = 4; else if (vp > 4) vp = 8;
-    p.vpad = 32 * vp;
+    p.vpad = 32 * vp;                                     // value columns of a block
+    p.raw_out = slices > 1 ? raw_out : nullptr;
     const int most = GLA_STATE_REGS / vp;                 // channels a warp can keep
     int parts = (dim + most - 1) / most;
     if (parts < 8) parts = dim < 8 ? dim : 8;             // eight warps where the sizes allow
-    FRB_CHECK_ARG(parts <= 16, "gla: a state of %d x %d per head is more than 512 threads keep in registers (32,768 elements)", dim, vdim);
     p.parts = parts;
     p.dchunk = (dim + parts - 1) / parts;
     p.dpad = p.parts * p.dchunk;
@@ -288,11 +339,11 @@ FRB_API int frb_gla_scan(const float* proj, int P, int off_q, int off_k, int off
     float* seg_first = segmented ? seg_scratch + (size_t)num_items * per_item : nullptr;
     p.seg_first = seg_first;
     p.seg_decay = segmented ? seg_scratch + 2 * (size_t)num_items * per_item : nullptr;
-    const dim3 grid(segmented ? num_items : num_seqs, heads), block(32 * parts);
+    const dim3 grid(segmented ? num_items : num_seqs, heads, slices), block(32 * parts);
 #define FRB_GLA_LAUNCH(VP)                                                                                            \
     do {                                                                                                              \
-        auto kernel = gla_scan_kernel<WT, OutT, VP, false>;                                                           \
-        auto local = gla_scan_kernel<WT, OutT, VP, true>;                                                             \
+        auto kernel = slices > 1 ? gla_scan_kernel<WT, OutT, VP, false, true> : gla_scan_kernel<WT, OutT, VP, false, false>; \
+        auto local = slices > 1 ? gla_scan_kernel<WT, OutT, VP, true, true> : gla_scan_kernel<WT, OutT, VP, true, false>;   \
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
         if (smem > 48 * 1024) cudaFuncSetAttribute(local, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);   \
         if (!segmented) {                                                                                             \
@@ -306,10 +357,14 @@ FRB_API int frb_gla_scan(const float* proj, int P, int off_q, int off_k, int off
             p.mode = GLA_OUTPUT;                                                                                      \
             kernel<<<grid, block, smem, stream>>>(p);                                                                 \
         }                                                                                                             \
+        if (p.raw_out)                                                                                                \
+            gla_finish_kernel<OutT><<<dim3(num_tokens, heads), 32, 0, stream>>>(p.raw_out, proj, norm_w, (OutT*)out, P, \
+                                                                               off_g, heads, vdim, eps);             \
     } while (0)
-    FRB_DISPATCH_DTYPE(weight_dtype, WT, FRB_DISPATCH_DTYPE(out_dtype, OutT, {
+    FRB_DISPATCH_DTYPE(out_dtype, OutT, {
+        typedef OutT WT;                                  // the decay's matrix is held in the type of the outputs
         if (vp == 1) FRB_GLA_LAUNCH(1); else if (vp == 2) FRB_GLA_LAUNCH(2); else if (vp == 4) FRB_GLA_LAUNCH(4); else FRB_GLA_LAUNCH(8);
-    }));
+    });
 #undef FRB_GLA_LAUNCH
     FRB_RETURN_LAUNCH("gla_scan");
 }

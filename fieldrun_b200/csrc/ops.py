@@ -29,7 +29,7 @@ _SIGNATURES = {
     "frb_layernorm": "ppppfppiii",
     "frb_unary_unit": "ppili",
     "frb_softcap": "plf",
-    "frb_gla_scan": "piiiiiipipppppppiiiiiifffppppip",
+    "frb_gla_scan": "piiiiiipipppppppiiiiiifffppppippi",
     "frb_router_topk": "ppiiiifpp",
     "frb_expert_plan": "piiiippppppp",
     "frb_expert_combine": "pppiiip",
@@ -298,10 +298,35 @@ def gla_scan(proj: torch.Tensor, offsets: tuple[int, int, int, int, int], a2: to
             raise KernelError("the table of the sequences' first segments needs one entry per sequence and one more")
         if scratch is None or scratch.dtype != torch.float32 or scratch.numel() < gla_scratch_floats(items, heads, dim, vdim):
             raise KernelError("a segmented scan needs float32 scratch of gla_scratch_floats(...) elements")
+    raw = None
+    if gla_value_slices(dim, vdim) > 1:
+        # the blocks of a head leave their columns of o here, unnormed; kept from call to call, so a recorded step
+        # finds it where it was
+        key = str(proj.device)
+        raw = _GLA_RAW.get(key)
+        if raw is None or raw.numel() < proj.shape[0] * heads * vdim:
+            if torch.cuda.is_current_stream_capturing():
+                raise KernelError("the buffer of a sliced recurrent state must exist before a step is recorded")
+            raw = _GLA_RAW[key] = torch.empty(max(proj.shape[0], 256) * heads * vdim, dtype=torch.float32, device=proj.device)
     _call("frb_gla_scan", _ptr(proj), proj.shape[1], *[int(o) for o in offsets], _ptr(a2), _code(a2.dtype), _ptr(a2_bias),
           _ptr(norm_weight), _ptr(state), _ptr(seq_slot), _ptr(seq_start), _ptr(cu_q_len), _ptr(out), _code(out.dtype),
           seq_slot.numel(), heads, dim, vdim, a2.shape[1], float(tau), float(q_scale), float(eps),
-          _ptr(seg[0]), _ptr(seg[1]), _ptr(seg[2]), _ptr(seg[3]), items, _ptr(scratch) if segments is not None else None)
+          _ptr(seg[0]), _ptr(seg[1]), _ptr(seg[2]), _ptr(seg[3]), items, _ptr(scratch) if segments is not None else None,
+          _ptr(raw), proj.shape[0])
+
+
+_GLA_RAW: dict[str, torch.Tensor] = {}
+
+
+def gla_value_slices(dim: int, vdim: int) -> int:
+    """Into how many slices of value columns :func:`gla_scan` cuts a head's state of ``dim`` x ``vdim`` (1 wherever a
+    block's registers hold it: up to 32,768 elements with padding)."""
+    fn = library("recurrent").frb_gla_value_slices
+    fn.restype, fn.argtypes = _I, [_I, _I]
+    slices = int(fn(int(dim), int(vdim)))
+    if slices == 0:
+        raise KernelError(f"gated linear attention: a state of {dim} x {vdim} per head is more than the kernel takes")
+    return slices
 
 
 def gla_scratch_floats(items: int, heads: int, dim: int, vdim: int) -> int:

@@ -250,7 +250,9 @@ def gla_case(rng, heads, dim, vdim, rank, width, tau, bias_shift):
 
 
 @pytest.mark.parametrize("heads,dim,vdim,rank,tau,shift", [(2, 16, 24, 5, 4.0, 0.0), (3, 8, 8, 3, 1.0, -3.0), (1, 100, 33, 2, 16.0, 4.0),
-                                                          (2, 128, 128, 16, 16.0, 2.0), (1, 200, 40, 4, 2.0, 0.0)])
+                                                          (2, 128, 128, 16, 16.0, 2.0), (1, 200, 40, 4, 2.0, 0.0),
+                                                          # states too large for one block: value columns in slices over blocks
+                                                          (1, 130, 200, 9, 32.0, 1.0), (2, 256, 300, 4, 4.0, 0.0)])
 def test_gated_linear_attention_scan_with_state_carried_between_calls(heads, dim, vdim, rank, tau, shift):
     rng = np.random.default_rng(dim + vdim)
     width = 48
@@ -286,7 +288,8 @@ def test_gated_linear_attention_scan_with_state_carried_between_calls(heads, dim
         close(f64(state[slots[b], n & 1]), states[b], 2e-5, f"state of sequence {b}")
 
 
-@pytest.mark.parametrize("heads,dim,vdim,rank,tau", [(2, 16, 24, 5, 4.0), (1, 128, 128, 16, 16.0), (3, 40, 70, 3, 1.0)])
+@pytest.mark.parametrize("heads,dim,vdim,rank,tau", [(2, 16, 24, 5, 4.0), (1, 128, 128, 16, 16.0), (3, 40, 70, 3, 1.0),
+                                                     (1, 300, 130, 4, 8.0)])
 def test_gated_linear_attention_in_segments_side_by_side(heads, dim, vdim, rank, tau):
     """A first call leaves a state; the second call's tokens are cut into segments of 128, 50 and 1 tokens that
     run side by side: outputs and the new state equal the plain recurrence over all tokens."""
