@@ -109,7 +109,9 @@ def test_a_step_that_wants_nothing_writes_no_file_and_a_full_cache_is_an_error(t
     from gpu_helpers import plain_weights
     config, weights = plain_weights("a")
     assert_close(out[1], pm.logits_all_positions(config, weights, [1, 2, 3, 4])[3:], "float32", "the token after a silent step")
-    text = json.dumps({"step": 0, "entries": [{"id": "y", "tokens": list(range(100)), "want": [99]}], "end": []}) + "\n"
+    # the runner adds room for the page padding of 64 requests to --max-tokens; a request beyond that is an error
+    long = [i % 200 for i in range(64 * 66)]
+    text = json.dumps({"step": 0, "entries": [{"id": "y", "tokens": long, "want": [len(long) - 1]}], "end": []}) + "\n"
     proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_folder("a"), "--dtype", "float32",
                            "--out", str(tmp_path / "p"), "--max-tokens", "64"], input=text, capture_output=True, text=True, timeout=600)
     assert proc.returncode != 0 and ("position tables end" in proc.stderr or "pages" in proc.stderr)
