@@ -632,3 +632,30 @@ def test_a_trace_replayed_through_the_runner(tmp_path, dtype):
         plain = plain_logits(name, n, 70 + i)
         got = np.stack([out[s][row] for s, row, _ in rows[k]])
         model_close(got, plain[[pos for _, _, pos in rows[k]]], dtype, f"request {k}")
+
+
+def test_command_line_generates_with_the_design(tmp_path):
+    """`python -m fieldrun_b200 random` writes a model of the design from a config.json, and the command line
+    generates from it what the plain model's greedy loop gives."""
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    config_path = tmp_path / "config.json"
+    config_path.write_text(json.dumps(ALL["B"][0]))
+    folder = tmp_path / "model"
+    made = subprocess.run([sys.executable, "-m", "fieldrun_b200", "random", "--config", str(config_path), "--seed", "9", "--std", "0.1",
+                           "--bias-std", "0.3", "-o", str(folder)], capture_output=True, text=True, cwd=root, timeout=300)
+    assert made.returncode == 0, made.stderr
+    with open(folder / "config.json") as handle:
+        config = json.load(handle)
+    from fieldrun_b200.weights.safetensors_io import ModelFolder
+    files = ModelFolder(str(folder))
+    weights = {n: files.tensor(n).double().numpy() for n in files.entries}
+    files.close()
+    ids = request_tokens("B", 20, 90)
+    (tmp_path / "ids.json").write_text(json.dumps(ids))
+    run = subprocess.run([sys.executable, "-m", "fieldrun_b200", "--model", str(folder), "--ids", str(tmp_path / "ids.json"), "--ctx", "12",
+                          "--generate", "6", "--dtype", "float32", "--eos", "none"], capture_output=True, text=True, cwd=root, timeout=600)
+    assert run.returncode == 0, run.stderr
+    want = ids[:12]
+    for _ in range(6):
+        want.append(int(np.argmax(pb.forward(config, weights, want)[-1])))
+    assert " ".join(str(t) for t in want[12:]) in run.stdout, run.stdout
