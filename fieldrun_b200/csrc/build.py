@@ -32,7 +32,8 @@ GROUPS: dict[str, tuple[str, ...]] = {
     "common": ("elementwise.cu", "layernorm.cu", "attention_generic.cu", "sampling.cu"),
     "attention": ("attention_mma.cu", "attention_decode_tma.cu", "attention_tc.cu"),
     "streams": ("experts_stream.cu", "experts_mma.cu"),
-    "experts": ("routing.cu", "experts_tc.cu", "experts_generic.cu"),
+    "experts": ("routing.cu", "experts_generic.cu"),
+    "products": ("experts_tc.cu",),
     "recurrent": ("gla.cu",),
     "extras": ("attention_decode_noalloc.cu", "wait_probe.cu"),
 }

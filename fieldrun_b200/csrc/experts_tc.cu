@@ -32,12 +32,22 @@ struct TcParams {
     void* out;
     int* status;             // 0, or the code of the wait that gave up
     int F, K, NT, stages, tmem_cols;
+    int activation;          // ACTIVE kernels: 0 relu(z)^2, 1 tanh-gelu, 2 silu, 3 relu, applied to a plain product's result
 };
+
+// The activations of a feed-forward of one product in and one out; the result is rounded to bfloat16.
+__device__ __forceinline__ float unit_activation(float z, int kind) {
+    if (kind == 0) { const float m = fmaxf(z, 0.f); return m * m; }
+    if (kind == 1) return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+    if (kind == 2) return __fdividef(z, 1.0f + __expf(-z));
+    return fmaxf(z, 0.f);
+}
 
 // WIDE (not PAIRED): the block takes 256 features, as two accumulators of 128 over the same rows: a stage then
 // feeds twice the arithmetic from the same tile of rows, which matters where the tiles come out of L2 as fast as
 // an SM can take them.
-template <bool PAIRED, bool WIDE, int EW, typename OutT>
+// ACTIVE (not PAIRED): the product's result goes through an activation on its way out (a dense feed-forward's first half).
+template <bool PAIRED, bool WIDE, int EW, typename OutT, bool ACTIVE = false>
 __global__ void __launch_bounds__(TC_THREADS(EW), EW == 4 ? 2 : 1)
 expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcParams p) {
     extern __shared__ uint8_t smem_raw[];
@@ -172,8 +182,13 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
                             float v = __uint_as_float(gate[half][j]);
                             // silu(gate) * up; the result is rounded to bfloat16, so the fast exponential and division do
                             if (PAIRED) v = __fdividef(v, 1.0f + __expf(-v)) * __uint_as_float(up[half][j]);
+                            if (ACTIVE) v = unit_activation(v, p.activation);
                             out[(size_t)(row0 + n) * p.F + f] = from_f32<OutT>(v);
-                            if (WIDE) out[(size_t)(row0 + n) * p.F + f + TC_FEATS] = from_f32<OutT>(__uint_as_float(up[half][j]));
+                            if (WIDE) {
+                                float second = __uint_as_float(up[half][j]);
+                                if (ACTIVE) second = unit_activation(second, p.activation);
+                                out[(size_t)(row0 + n) * p.F + f + TC_FEATS] = from_f32<OutT>(second);
+                            }
                         }
                     }
                 }
@@ -202,8 +217,10 @@ expert_gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_co
 // order); tiles of tile_rows = 32, 64, 128 or 256 rows.  status: one int on the device, zero before the call.
 FRB_API int frb_expert_gemm_tc(const void* W, int num_experts, const void* X, int x_rows_total, const int* tile_expert,
                                const int* tile_row0, const int* num_tiles, const int* offsets, int max_tiles, int tile_rows,
-                               void* out, int F, int K, int paired, int* status, cudaStream_t stream) {
+                               void* out, int F, int K, int paired, int* status, int activation, cudaStream_t stream) {
     if (max_tiles == 0) return 0;
+    FRB_CHECK_ARG(activation >= -1 && activation <= 3 && !(paired && activation >= 0),
+                  "expert tensor-core product: activation %d (none is -1; a paired product has its gate)", activation);
     FRB_CHECK_ARG(K % TC_KBLOCK == 0 && K > 0, "expert tensor-core product: inner size %d is not a multiple of 64", K);
     FRB_CHECK_ARG(F % TC_FEATS == 0 && F > 0, "expert tensor-core product: %d features are not a multiple of 128", F);
     FRB_CHECK_ARG(tile_rows == 32 || tile_rows == 64 || tile_rows == 128 || tile_rows == 256,
@@ -215,7 +232,7 @@ FRB_API int frb_expert_gemm_tc(const void* W, int num_experts, const void* X, in
                   "expert tensor-core product: cuTensorMapEncodeTiled failed or is not available");
     TcParams p;
     p.tile_expert = tile_expert; p.tile_row0 = tile_row0; p.num_tiles = num_tiles; p.offsets = offsets; p.out = out;
-    p.status = status; p.F = F; p.K = K; p.NT = tile_rows;
+    p.status = status; p.F = F; p.K = K; p.NT = tile_rows; p.activation = activation;
     // products of one matrix take 256 features a block where the tiles are large and arithmetic is the bound
     const bool wide = !paired && tile_rows >= 128 && F % (2 * TC_FEATS) == 0;
     const bool two = paired || wide;
@@ -235,13 +252,15 @@ FRB_API int frb_expert_gemm_tc(const void* W, int num_experts, const void* X, in
     cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, device);
     const long long resident = (long long)sms * (two_per_sm ? 2 : 1);           // the blocks stay; each takes every resident-th item
     dim3 grid((unsigned)(most_items < resident ? most_items : resident));
-#define FRB_TC_LAUNCH(PAIRED, WIDE, EW, OutT)                                                                              \
+#define FRB_TC_LAUNCH(PAIRED, WIDE, EW, ...)                                                                               \
     do {                                                                                                                   \
-        cudaFuncSetAttribute(expert_gemm_tc_kernel<PAIRED, WIDE, EW, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        launch_dependent_resident(EW == 4 ? 2 : 1, expert_gemm_tc_kernel<PAIRED, WIDE, EW, OutT>, grid, dim3(TC_THREADS(EW)), smem, \
+        cudaFuncSetAttribute(expert_gemm_tc_kernel<PAIRED, WIDE, EW, __VA_ARGS__>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_dependent_resident(EW == 4 ? 2 : 1, expert_gemm_tc_kernel<PAIRED, WIDE, EW, __VA_ARGS__>, grid, dim3(TC_THREADS(EW)), smem, \
                                   stream, map_w, map_x, p);                                                                 \
     } while (0)
     if (paired) { if (two_per_sm) FRB_TC_LAUNCH(true, false, 4, bf16); else FRB_TC_LAUNCH(true, false, 8, bf16); }
+    else if (activation >= 0 && wide) { if (two_per_sm) FRB_TC_LAUNCH(false, true, 4, bf16, true); else FRB_TC_LAUNCH(false, true, 8, bf16, true); }
+    else if (activation >= 0) { if (two_per_sm) FRB_TC_LAUNCH(false, false, 4, bf16, true); else FRB_TC_LAUNCH(false, false, 8, bf16, true); }
     else if (wide) { if (two_per_sm) FRB_TC_LAUNCH(false, true, 4, float); else FRB_TC_LAUNCH(false, true, 8, float); }
     else { if (two_per_sm) FRB_TC_LAUNCH(false, false, 4, float); else FRB_TC_LAUNCH(false, false, 8, float); }
 #undef FRB_TC_LAUNCH

@@ -46,7 +46,7 @@ _SIGNATURES = {
     "frb_route_plan_small": "ppiiiifipppppppp",
     "frb_router_small": "ppipppiiiifipppppppp",
     "frb_router_logits": "ppiiip",
-    "frb_expert_gemm_tc": "pipippppiipiiip",
+    "frb_expert_gemm_tc": "pipippppiipiiipi",
     "frb_gather_rows_bf16": "pppii",
     "frb_attention_prefill_tc": "pippipippipppppiiifipp",
 }
@@ -64,7 +64,8 @@ _ENTRY_GROUPS = {
     "attention": ("frb_attention_decode_mma", "frb_attention_prefill_mma", "frb_attention_decode_tma", "frb_attention_prefill_tc"),
     "streams": ("frb_weight_stream", "frb_expert_gemm_mma"),
     "experts": ("frb_router_topk", "frb_expert_plan", "frb_expert_combine", "frb_expert_gemm_generic", "frb_route_plan_small",
-                "frb_router_small", "frb_router_logits", "frb_expert_gemm_tc", "frb_gather_rows_bf16"),
+                "frb_router_small", "frb_router_logits"),
+    "products": ("frb_expert_gemm_tc", "frb_gather_rows_bf16"),
     "recurrent": ("frb_gla_scan",),
     "extras": ("frb_wait_probe",),
 }
@@ -751,15 +752,20 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor, out: torch.Tensor) -> None:
 
 def expert_gemm_tc(w: torch.Tensor, x: torch.Tensor, tile_expert: torch.Tensor, tile_row0: torch.Tensor,
                    num_tiles: torch.Tensor, offsets: torch.Tensor, max_tiles: int, tile_rows: int, out: torch.Tensor, *,
-                   paired: bool) -> None:
+                   paired: bool, activation: Optional[str] = None) -> None:
     """The expert products on tcgen05 tensor cores; x holds the rows in expert-sorted order (tiles of 32, 64,
-    128 or 256 rows; features in steps of 128, inner size in steps of 64)."""
+    128 or 256 rows; features in steps of 128, inner size in steps of 64).  A plain product may send its result
+    through an ``activation`` (a key of ``ACTIVATIONS``) on the way out, in bfloat16: the first half of a dense
+    feed-forward, the whole step being one expert."""
     _want(w, torch.bfloat16, "expert weights")
     _want(x, torch.bfloat16, "expert inputs")
-    _want(out, torch.bfloat16 if paired else torch.float32, "expert outputs")
+    if activation is not None and (paired or activation not in ACTIVATIONS):
+        raise KernelError(f"activation {activation!r} on a {'paired' if paired else 'plain'} product")
+    _want(out, torch.bfloat16 if paired or activation is not None else torch.float32, "expert outputs")
     feats = w.shape[1] // 2 if paired else w.shape[1]
     _call("frb_expert_gemm_tc", _ptr(w), w.shape[0], _ptr(x), x.shape[0], _ptr(tile_expert), _ptr(tile_row0), _ptr(num_tiles),
-          _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), _ptr(tc_status(w.device)))
+          _ptr(offsets), max_tiles, tile_rows, _ptr(out), feats, w.shape[2], int(paired), _ptr(tc_status(w.device)),
+          ACTIVATIONS[activation] if activation is not None else -1)
 
 
 _ROUTER_TICKETS: dict[str, torch.Tensor] = {}

@@ -31,7 +31,7 @@ TENSOR_CORE_ROWS_PER_EXPERT = {"decode": 4.0, "prompt": 1.0}
 
 
 class RoutedExperts(FeedForward):
-    kernel_groups = ("common", "streams", "experts")
+    kernel_groups = ("common", "streams", "experts", "products")
 
     wants_float32_input = True          # the router reads the normed rows before they are rounded
     replayable = True
@@ -270,11 +270,17 @@ class DenseGatedUnit(FeedForward):
         return linear(hidden, self.w_down)
 
 
+FUSED_ACTIVATION_ROWS = 64      # from this many rows of a prompt step on, a dense unit's first product carries its activation
+
+
 class DenseUnit(FeedForward):
     """W_down act(W_up x): one product in, an activation, one product out.  ``activation`` is one of
-    ``ops.ACTIVATIONS`` (``relu_squared``: relu(z)^2, ``gelu_tanh``, ``silu``, ``relu``)."""
+    ``ops.ACTIVATIONS`` (``relu_squared``: relu(z)^2, ``gelu_tanh``, ``silu``, ``relu``).  A prompt's rows in bfloat16
+    take the first product on tcgen05 with the activation in its epilogue (the step as one expert's rows); few rows,
+    float32 and sizes that kernel does not take go through the plain product and the activation kernel."""
 
     replayable = True
+    kernel_groups = ("common", "streams", "products")
 
     def __init__(self, spec, dtype):
         super().__init__(spec, dtype)
@@ -285,6 +291,7 @@ class DenseUnit(FeedForward):
             raise ValueError(f"activation {self.activation!r} is none of {sorted(ops.ACTIVATIONS)}")
         self.w_up: Optional[torch.Tensor] = None
         self.w_down: Optional[torch.Tensor] = None
+        self._tiles: dict = {}
 
     def _needs(self):
         d, i = self.hidden_size, self.width
@@ -297,10 +304,33 @@ class DenseUnit(FeedForward):
     def load(self, source: TensorSource) -> None:
         self.w_up, self.w_down = (source.fetch(n) for n in self._needs())
 
+    def fused_tiles(self, ctx, rows: int):
+        """The lists that make the step one expert's rows in tiles, for the tcgen05 product; they depend on the number
+        of rows alone and are kept."""
+        tile_rows = 256 if rows >= 256 else 128 if rows > 64 else 64 if rows > 32 else 32
+        key = (str(ctx.device), rows)
+        made = self._tiles.get(key)
+        if made is None:
+            if len(self._tiles) > 64:
+                self._tiles.clear()
+            count = (rows + tile_rows - 1) // tile_rows
+            flat = torch.tensor([0] * count + [tile_rows * i for i in range(count)] + [count, 0, rows], dtype=torch.int32).to(ctx.device)
+            made = self._tiles[key] = (flat[:count], flat[count:2 * count], flat[2 * count:2 * count + 1], flat[2 * count + 1:], count,
+                                       tile_rows)
+        return made
+
     def forward(self, ctx, act, act32):
-        up = linear(act, self.w_up)                                # float32 [T, I]
-        hidden = ctx.buffer("dense.hidden", (act.shape[0], self.width), self.dtype)
-        ops.unary_unit(up, hidden, self.activation)
+        rows = act.shape[0]
+        hidden = ctx.buffer("dense.hidden", (rows, self.width), self.dtype)
+        if (self.dtype == torch.bfloat16 and rows >= FUSED_ACTIVATION_ROWS and not ctx.is_decode and self.width % 128 == 0
+                and self.hidden_size % 64 == 0):
+            # a prompt's rows: product and activation in one kernel on tcgen05, the result rounded once to bfloat16
+            tile_expert, tile_row0, num_tiles, offsets, count, tile_rows = self.fused_tiles(ctx, rows)
+            ops.expert_gemm_tc(self.w_up.view(1, self.width, self.hidden_size), act, tile_expert, tile_row0, num_tiles, offsets,
+                               count, tile_rows, hidden, paired=False, activation=self.activation)
+        else:
+            up = linear(act, self.w_up)                            # float32 [T, I]
+            ops.unary_unit(up, hidden, self.activation)
         return linear(hidden, self.w_down)
 
 

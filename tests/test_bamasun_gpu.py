@@ -118,6 +118,26 @@ def test_activations_and_logit_cap():
     close(f64(logits), pb.softcap(z * 20, 30.0), 1e-6)
 
 
+@pytest.mark.parametrize("rows,inner,features", [(300, 128, 256), (64, 64, 128), (1000, 192, 384), (257, 256, 1024)])
+@pytest.mark.parametrize("activation", ["relu_squared", "gelu_tanh", "silu"])
+def test_first_product_of_a_dense_unit_with_its_activation_on_tcgen05(rows, inner, features, activation):
+    """The whole step as one expert's rows in tiles: act(x W^T) rounded once to bfloat16."""
+    rng = np.random.default_rng(rows + features)
+    x = dev(rng.normal(size=(rows, inner)), torch.bfloat16)
+    w = dev(rng.normal(size=(features, inner)) * inner ** -0.5, torch.bfloat16)
+    z = f64(x) @ f64(w).T
+    want = {"relu_squared": np.maximum(z, 0) ** 2, "silu": pb.silu(z),
+            "gelu_tanh": 0.5 * z * (1 + np.tanh(np.sqrt(2 / np.pi) * (z + 0.044715 * z ** 3)))}[activation]
+    for tile_rows in (32, 64, 128, 256):
+        count = (rows + tile_rows - 1) // tile_rows
+        out = torch.full((rows, features), 7.0, dtype=torch.bfloat16, device=DEV)
+        ops().expert_gemm_tc(w.view(1, features, inner), x, dev(np.zeros(count, dtype=np.int32)),
+                             dev((np.arange(count) * tile_rows).astype(np.int32)), dev(np.array([count], dtype=np.int32)),
+                             dev(np.array([0, rows], dtype=np.int32)), count, tile_rows, out, paired=False, activation=activation)
+        ops().tc_status_check(DEV)
+        close(f64(out), want, 1.2e-2, f"tiles of {tile_rows}")
+
+
 def scrambled_pages(rng, slots, lengths, kv_heads, dim, vdim, dtype, spare=3):
     """Keys [slot][T, G, dim], values [slot][T, G, vdim] laid into pages in a scrambled order."""
     per = [(n + 63) // 64 for n in lengths]
