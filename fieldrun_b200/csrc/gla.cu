@@ -136,10 +136,23 @@ __global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
             s_v[t * vpad + c] = rows[(size_t)t * p.P + p.off_v + h * vdim + v0 + c];
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < count * dim; i += nthreads) {
+        // four (token, channel) pairs a thread at a time: their loads go out together, then the arithmetic
+        for (int base = 0; base < count * dim; base += 4 * nthreads) {
+          float q4[4], k4[4];
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = base + u * nthreads + threadIdx.x;
             const int t = i / dim, d = i - t * dim;
-            const float qv = LOCAL ? 0.f : rows[(size_t)t * p.P + p.off_q + h * dim + d] * p.q_scale;
-            const float kv = rows[(size_t)t * p.P + p.off_k + h * dim + d];
+            const bool in = i < count * dim;
+            q4[u] = (LOCAL || !in) ? 0.f : rows[(size_t)t * p.P + p.off_q + h * dim + d];
+            k4[u] = in ? rows[(size_t)t * p.P + p.off_k + h * dim + d] : 0.f;
+          }
+#pragma unroll
+          for (int u = 0; u < 4; ++u) {
+            const int i = base + u * nthreads + threadIdx.x;
+            if (i >= count * dim) break;
+            const int t = i / dim, d = i - t * dim;
+            const float qv = q4[u] * p.q_scale, kv = k4[u];
             float z = a2_bias[d];
             const float* a1 = s_a1 + t * rank;
             if (p.a2_shared && (rank & 3) == 0) {
@@ -161,6 +174,7 @@ __global__ void __launch_bounds__(512) gla_scan_kernel(GlaParams p) {
             }
             const float la = log_sigmoid(z) * p.inv_tau;
             s_qka[t * dpad + d] = make_float4(qv, kv, expf(la), la);
+          }
         }
         __syncthreads();
         if (LOCAL)
