@@ -140,8 +140,13 @@ def main() -> int:
         args.warmup = 3
     if args.design is not None:
         from fieldrun_b200.compare import compare_designs
+        sampler = ClockSampler()
+        sampler.start()
+        began = time.time()
         out = compare_designs(tuple(args.sizes.split(",")), steps=min(args.steps, 16), warmup=args.warmup)
-        out.update({"design": args.design, "n_gpus": 1, "peaks": peaks()[0], "peaks_source": peaks()[1]})
+        out.update({"design": args.design, "n_gpus": 1, "peaks": peaks()[0], "peaks_source": peaks()[1],
+                    "clocks": sampler.window(began, time.time())})
+        sampler.stop()
         print(json.dumps(out))
         return 0
 
