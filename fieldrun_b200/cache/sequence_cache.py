@@ -6,9 +6,10 @@ The reference allocates, per ``generate`` call and for its single sequence, two
 sequences of unequal, growing lengths share one store, so the store is cut into
 pages: a sequence holds ``ceil(length / 64)`` pages per group and a table maps
 (slot, position // 64) to a page.  Cache lines whose needs are the same (number
-of key/value heads, key and value head sizes, all keys or a window of them) form a *group* with
+of key/value heads, key and value head sizes, all keys, a window of them or chunks) form a *group* with
 a store, a page pool and a table of its own; a windowed group gives a page back
-as soon as every key on it lies outside the window.  What is cached is K after
+as soon as every key on it lies outside the window, a chunked group as soon as the
+sequence has left the chunks that the page holds.  What is cached is K after
 norm and rotary and V as projected (src/minimax.rs:262-268).
 
 The state area holds, per cache line that asks for one, a tensor of a fixed
@@ -37,12 +38,13 @@ class CacheNeed:
     head_dim: int = 0
     window: int | None = None            # None: every earlier key stays visible
     value_dim: int = 0                   # size of a value head; 0: the keys' head_dim
+    chunk: int | None = None             # a query sees only the keys of its own chunk of this many positions
     state_shape: tuple[int, ...] = ()    # state per sequence; () for none
     state_dtype: str = "float32"         # "float32" | "bfloat16" | "int32"
 
     @property
-    def group_key(self) -> tuple[int, int, int | None, int] | None:
-        return (self.kv_heads, self.head_dim, self.window, self.value_dim or self.head_dim) if self.kv_heads else None
+    def group_key(self) -> tuple | None:
+        return (self.kv_heads, self.head_dim, self.window, self.value_dim or self.head_dim, self.chunk) if self.kv_heads else None
 
 
 def pages_for(tokens: int) -> int:
@@ -62,7 +64,7 @@ class LineView:
 
 class _Group:
     def __init__(self, key, lines, num_pages, num_slots, dtype, device, allocate):
-        self.kv_heads, self.head_dim, self.window, self.value_dim = key
+        self.kv_heads, self.head_dim, self.window, self.value_dim, self.chunk = key
         self.lines = list(lines)
         self.num_pages = num_pages
         self.pool = IndexPool(num_pages, "page")
@@ -99,10 +101,15 @@ class _Group:
             self.fresh.append(int(self.table[slot, hi - 1]))
 
     def release_outside_window(self, slot: int, length: int) -> None:
-        if self.window is None:
+        if self.window is None and self.chunk is None:
             return
-        # the next query sits at position >= length and sees keys j > position - window
-        first_needed = max(0, length - self.window + 1) // PAGE_TOKENS
+        first_needed = 0
+        if self.window is not None:
+            # the next query sits at position >= length and sees keys j > position - window
+            first_needed = max(0, length - self.window + 1) // PAGE_TOKENS
+        if self.chunk is not None:
+            # ... and only keys of its own chunk, which begins at or after the chunk of position `length`
+            first_needed = max(first_needed, (length // self.chunk * self.chunk) // PAGE_TOKENS)
         lo = int(self.first_page[slot])
         hi = min(first_needed, int(self.end_page[slot]))
         if hi <= lo:
@@ -220,7 +227,7 @@ class SequenceCache:
         for slot, n in zip(slots, new_tokens):
             self.lengths[slot] += n
         for group in self.groups:
-            if group.window is not None:
+            if group.window is not None or group.chunk is not None:
                 for slot in slots:
                     group.release_outside_window(slot, self.length(slot))
                 group.sync()

@@ -42,11 +42,14 @@ class RunSpec:
     """One entry of the run order.  ``layer`` indexes :attr:`ModelPlan.layers`
     (the same layer may run twice).  ``cache_line`` names the line of the cache
     this run reads; ``writes_cache`` is false for a run that reads a line which
-    an earlier run wrote."""
+    an earlier run wrote.  ``connector`` names a part that rewrites the whole stream before the run (a model
+    that runs a stretch of layers several times mixes the embedding back in at the start of every pass)."""
 
     layer: int
     cache_line: int
     writes_cache: bool = True
+    # (index into ModelPlan.connectors, number of the pass): the stream goes through that connector before this run
+    connector: Optional[tuple[int, int]] = None
 
 
 @dataclass(frozen=True)
@@ -60,10 +63,14 @@ class ModelPlan:
     final_norm: PartSpec
     head: PartSpec
     eos_token_id: tuple[int, ...] = ()
+    connectors: tuple[PartSpec, ...] = ()
 
     def check(self) -> None:
         written: set[int] = set()
         for step, run in enumerate(self.run_order):
+            if run.connector is not None and not 0 <= run.connector[0] < len(self.connectors):
+                raise ValueError(f"run order entry {step} names connector {run.connector[0]}, the plan has "
+                                 f"{len(self.connectors)}")
             if not 0 <= run.layer < len(self.layers):
                 raise ValueError(f"run order entry {step} names layer {run.layer}, the plan has {len(self.layers)}")
             if run.writes_cache:

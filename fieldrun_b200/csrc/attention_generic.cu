@@ -8,7 +8,10 @@
 // the reference's -1e30 amounts to after the exponential.
 // Two things the reference's model does not have are arguments here: a value head of another size than the
 // key head (v_dim), and a bias on the score that grows with the distance, s_j -= slope[h] * (i - j) for the query
-// at position i (a slope per query head; null: none).
+// at position i (a slope per query head; null: none).  Three more, each off unless given: `chunk` (the query at i
+// sees only keys of its own chunk, floor(j / chunk) == floor(i / chunk), chunks counted from position 0), `sinks`
+// (a number per query head whose exponential joins the softmax's denominator, with no key and no value: it is not
+// scaled and counts once) and `gate` (the head's output is multiplied by sigmoid(gate[t, h])).
 #include "common.cuh"
 
 struct AttnParams {
@@ -16,6 +19,9 @@ struct AttnParams {
     const void* k_pages;      // [pages, nkv, PAGE, hd]
     const void* v_pages;      // [pages, nkv, vd, PAGE]: values lie transposed within a page
     const float* slopes;      // [nh] or null
+    const float* sinks;       // [nh] or null
+    const float* gate;        // [T, gate_stride] or null: head h of token t at t * gate_stride + h
+    int chunk, gate_stride;   // chunk 0: no chunks
     const int* page_table;    // [slots, max_pages]
     const int* tok_pos;       // [T]
     const int* tok_slot;      // [T]
@@ -40,7 +46,8 @@ __global__ void attention_generic_kernel(AttnParams p) {
     const int group = p.num_heads / p.num_kv_heads;
     const int pos = p.tok_pos[t];
     const int hi = pos;
-    const int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    int lo = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    if (p.chunk > 0) lo = max(lo, pos / p.chunk * p.chunk);
     const int* table = p.page_table + (size_t)p.tok_slot[t] * p.max_pages;
     const T* q = (const T*)p.q;
     const T* k_pages = (const T*)p.k_pages;
@@ -102,7 +109,16 @@ __global__ void attention_generic_kernel(AttnParams p) {
             }
         }
         if (active) {
-            const float inv = 1.0f / l;
+            if (p.sinks) {
+                const float sink = p.sinks[head];
+                const float m_new = fmaxf(m, sink);
+                const float corr = expf(m - m_new);
+                l = l * corr + expf(sink - m_new);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[i] *= corr;
+            }
+            float inv = 1.0f / l;
+            if (p.gate) inv *= 1.0f / (1.0f + expf(-p.gate[(size_t)t * p.gate_stride + head]));
 #pragma unroll
             for (int i = 0; i < 8; ++i) {
                 const int d = lane + 32 * i;
@@ -115,7 +131,8 @@ __global__ void attention_generic_kernel(AttnParams p) {
 FRB_API int frb_attention_generic(const void* q, const void* k_pages, const void* v_pages, int dtype,
                                   const int* page_table, int max_pages, const int* tok_pos, const int* tok_slot,
                                   void* out, int num_tokens, int num_heads, int num_kv_heads, int head_dim,
-                                  float scale, int window, int v_dim, const float* slopes, cudaStream_t stream) {
+                                  float scale, int window, int v_dim, const float* slopes, int chunk, const float* sinks,
+                                  const float* gate, int gate_stride, cudaStream_t stream) {
     if (num_tokens == 0) return 0;
     if (v_dim <= 0) v_dim = head_dim;
     FRB_CHECK_ARG(v_dim <= 256, "attention: v_dim %d is outside 1..256", v_dim);
@@ -127,6 +144,7 @@ FRB_API int frb_attention_generic(const void* q, const void* k_pages, const void
     p.q = q; p.k_pages = k_pages; p.v_pages = v_pages; p.page_table = page_table; p.tok_pos = tok_pos;
     p.tok_slot = tok_slot; p.out = out; p.scale = scale; p.window = window; p.max_pages = max_pages;
     p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.head_dim = head_dim; p.v_dim = v_dim; p.slopes = slopes;
+    p.chunk = chunk; p.sinks = sinks; p.gate = gate; p.gate_stride = gate_stride;
     const int group = num_heads / num_kv_heads;
     const int nwarps = group < 8 ? group : 8;
     const size_t smem = ((size_t)KEY_BLOCK * (head_dim + 1) + (size_t)KEY_BLOCK * v_dim + (size_t)nwarps * head_dim) * sizeof(float);

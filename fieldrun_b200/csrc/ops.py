@@ -25,10 +25,20 @@ _SIGNATURES = {
     "frb_qkv_prepare": "pippifppipppipppiiiiiiiiiipifi",
     "frb_wait_probe": "lpp",
     "frb_add_rows": "ppl",
-    "frb_attention_generic": "pppipipppiiiifiip",
+    "frb_attention_generic": "pppipipppiiiifiipippi",
     "frb_layernorm": "ppppfppiii",
     "frb_unary_unit": "ppili",
     "frb_softcap": "plf",
+    "frb_dyt_norm": "ppppppippppppppppiiii",
+    "frb_rms_blend": "pppppiiff",
+    "frb_concat_rows": "ppppiiii",
+    "frb_add_row_vector": "pppii",
+    "frb_head_gate": "pipiiii",
+    "frb_causal_conv": "piippppppppllppiiiii",
+    "frb_selective_scan": "piippiiippppppppllpiiii",
+    "frb_gated_recurrence": "piippppppppppllpiiiiif",
+    "frb_state_space_scan": "piiipiiipppppppllpiiiii",
+    "frb_group_rms_norm": "pppiiiif",
     "frb_gla_scan": "piiiiiipipppppppiiiiiifffppppippi",
     "frb_router_topk": "ppiiiifpp",
     "frb_expert_plan": "piiiippppppp",
@@ -60,13 +70,15 @@ class KernelError(RuntimeError):
 # which library of kernels (a group of build.GROUPS) holds which entry point
 _ENTRY_GROUPS = {
     "common": ("frb_embed_rows", "frb_rmsnorm", "frb_qkv_prepare", "frb_add_rows", "frb_attention_generic", "frb_layernorm",
-               "frb_unary_unit", "frb_softcap", "frb_gated_unit", "frb_sample_rows", "frb_argmax_rows", "frb_sample_floor"),
+               "frb_unary_unit", "frb_softcap", "frb_gated_unit", "frb_sample_rows", "frb_argmax_rows", "frb_sample_floor",
+               "frb_dyt_norm", "frb_rms_blend", "frb_concat_rows", "frb_add_row_vector", "frb_head_gate"),
     "attention": ("frb_attention_decode_mma", "frb_attention_prefill_mma", "frb_attention_decode_tma", "frb_attention_prefill_tc"),
     "streams": ("frb_weight_stream", "frb_expert_gemm_mma"),
     "experts": ("frb_router_topk", "frb_expert_plan", "frb_expert_combine", "frb_expert_gemm_generic", "frb_route_plan_small",
                 "frb_router_small", "frb_router_logits"),
     "products": ("frb_expert_gemm_tc", "frb_gather_rows_bf16"),
     "recurrent": ("frb_gla_scan",),
+    "scans": ("frb_causal_conv", "frb_selective_scan", "frb_gated_recurrence", "frb_state_space_scan", "frb_group_rms_norm"),
     "extras": ("frb_wait_probe",),
 }
 _GROUP_OF = {entry: group for group, entries in _ENTRY_GROUPS.items() for entry in entries}
@@ -319,6 +331,162 @@ def gla_scan(proj: torch.Tensor, offsets: tuple[int, int, int, int, int], a2: to
 _GLA_RAW: dict[str, torch.Tensor] = {}
 
 
+# ------------------------------------------------------------------------------------------------ stream operations
+
+def dyt_norm(x: torch.Tensor, first: tuple[torch.Tensor, torch.Tensor, torch.Tensor], out1: torch.Tensor, *,
+             second: Optional[tuple[torch.Tensor, torch.Tensor, torch.Tensor]] = None, out2: Optional[torch.Tensor] = None,
+             out2_32: Optional[torch.Tensor] = None, deltas: tuple = (), experts=None, rows: Optional[torch.Tensor] = None,
+             write_back: bool = False) -> None:
+    """Dynamic tanh of v = x + updates: out1 = tanh(alpha v) * w + b with ``first`` = (w, b, alpha), and the same with
+    ``second`` into ``out2`` (and ``out2_32`` in float32) when a second norm reads the same v.  ``deltas``: up to two
+    float32 tensors [T, width]; ``experts`` = (y, weights, row_of_assign) as for :func:`rmsnorm`; the sum is stored back
+    into x when ``write_back``.  ``rows`` picks the rows to norm (then nothing is stored back).  ``alpha`` is a float32
+    tensor of one element on the device."""
+    _want(x, torch.float32, "the residual stream")
+    for t in (*first, *(second or ())):
+        _want(t, torch.float32, "a dynamic-tanh norm's weight, bias or alpha")
+    deltas = tuple(d for d in deltas if d is not None)
+    if len(deltas) > 2:
+        raise KernelError("dyt_norm adds at most two tensors")
+    for d in deltas:
+        _want(d, torch.float32, "the residual update")
+        if d.shape != x.shape:
+            raise KernelError("an update of another shape than the stream")
+    d0 = deltas[0] if len(deltas) > 0 else None
+    d1 = deltas[1] if len(deltas) > 1 else None
+    y = ew = rowmap = None
+    top_k = 0
+    if experts is not None:
+        y, ew, rowmap = experts
+        _want(y, torch.float32, "expert outputs")
+        _want(ew, torch.float32, "expert weights")
+        _want(rowmap, torch.int32, "rows of the assignments")
+        top_k = ew.shape[-1]
+    if rows is not None:
+        _want(rows, torch.int32, "row indices")
+    if second is not None and (out2 is None or out2.dtype != out1.dtype):
+        raise KernelError("the second norm needs an output of the first one's dtype")
+    if out2_32 is not None:
+        _want(out2_32, torch.float32, "the 32-bit copy")
+    num_rows = rows.numel() if rows is not None else x.shape[0]
+    w2, b2, a2 = second if second is not None else (None, None, None)
+    _call("frb_dyt_norm", _ptr(x), _ptr(d0), _ptr(d1), _ptr(y), _ptr(ew), _ptr(rowmap), top_k, _ptr(rows), _ptr(first[0]),
+          _ptr(first[1]), _ptr(first[2]), _ptr(out1), _ptr(w2), _ptr(b2), _ptr(a2), _ptr(out2), _ptr(out2_32),
+          _code(out1.dtype), num_rows, x.shape[-1], int(write_back))
+
+
+def rms_blend(a: torch.Tensor, b: torch.Tensor, wa: torch.Tensor, wb: torch.Tensor, out: torch.Tensor, eps: float,
+              share: float) -> None:
+    """out = share * (a / rms(a) * wa + b / rms(b) * wb), row by row, all float32."""
+    for t in (a, b, wa, wb, out):
+        _want(t, torch.float32, "rms_blend's rows and weights")
+    if a.shape != b.shape or a.shape != out.shape:
+        raise KernelError("rms_blend: rows of unequal shapes")
+    _call("frb_rms_blend", _ptr(a), _ptr(b), _ptr(wa), _ptr(wb), _ptr(out), a.shape[0], a.shape[1], float(eps), float(share))
+
+
+def concat_rows(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor, delta: Optional[torch.Tensor] = None) -> None:
+    """out[t] = [a[t] (+ delta[t]) | b[t]] in out's dtype; a, b, delta float32."""
+    _want(a, torch.float32, "rows")
+    _want(b, torch.float32, "rows")
+    if delta is not None:
+        _want(delta, torch.float32, "the update")
+    if out.shape[1] != a.shape[1] + b.shape[1]:
+        raise KernelError("concat_rows: the output's width is not the sum of the inputs'")
+    _call("frb_concat_rows", _ptr(a), _ptr(delta), _ptr(b), _ptr(out), _code(out.dtype), a.shape[0], a.shape[1], b.shape[1])
+
+
+def add_row_vector(y: torch.Tensor, vec: torch.Tensor, out: torch.Tensor) -> None:
+    """out[t] = y[t] + vec, float32."""
+    for t in (y, vec, out):
+        _want(t, torch.float32, "add_row_vector's operands")
+    if vec.numel() != y.shape[1] or out.shape != y.shape:
+        raise KernelError("add_row_vector: shapes do not fit")
+    _call("frb_add_row_vector", _ptr(y), _ptr(vec), _ptr(out), y.shape[0], y.shape[1])
+
+
+def head_gate(out: torch.Tensor, gate: torch.Tensor, heads: int, vdim: int) -> None:
+    """out[t, h, :] *= sigmoid(gate[t, h]) in place; ``gate`` float32 [T, >= heads]."""
+    _want(gate, torch.float32, "head gates")
+    _call("frb_head_gate", _ptr(out), _code(out.dtype), _ptr(gate), gate.shape[1], out.shape[0], heads, vdim)
+
+
+# ------------------------------------------------------------------------------------------------ recurrences
+
+CONV_ACTIVATIONS = {None: 0, "none": 0, "silu": 1}
+
+
+def _state_place(state: torch.Tensor, offset: int) -> tuple:
+    _want(state, torch.float32, "the recurrent state")
+    if state.dim() != 3 or state.shape[1] != 2:
+        raise KernelError(f"the recurrent state is {list(state.shape)}, not [slots, 2, floats]")
+    return _ptr(state), int(state.shape[2]), int(offset)
+
+
+def causal_conv(rows_in: torch.Tensor, in_offset: int, channels: int, taps: torch.Tensor, bias: Optional[torch.Tensor],
+                ctx, state: torch.Tensor, state_offset: int, out32: torch.Tensor, out_typed: Optional[torch.Tensor] = None, *,
+                in_bias: Optional[torch.Tensor] = None, activation: Optional[str] = None) -> None:
+    """A causal convolution per channel over the step's new tokens (see scans.cu): channel c reads column
+    ``in_offset + c`` of the float32 ``rows_in``; ``taps`` float32 [channels, K]; the K-1 inputs before a step's first
+    token come from ``state`` ([slots, 2, floats], this convolution's part at ``state_offset``: [K-1, channels]), and
+    the step's last K-1 inputs are left there.  ``ctx`` gives the step's tables."""
+    _want(rows_in, torch.float32, "the convolution's input")
+    _want(taps, torch.float32, "the convolution's taps")
+    _want(out32, torch.float32, "the convolution's output")
+    if taps.shape[0] != channels or activation not in CONV_ACTIVATIONS:
+        raise KernelError("causal_conv: taps of another size than the channels, or an unknown activation")
+    _call("frb_causal_conv", _ptr(rows_in), rows_in.shape[1], int(in_offset), _ptr(in_bias), _ptr(taps), _ptr(bias),
+          _ptr(ctx.tok_seq), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.cu_q_len), *_state_place(state, state_offset),
+          _ptr(out32), _ptr(out_typed), _code(out_typed.dtype) if out_typed is not None else 0, rows_in.shape[0], channels,
+          taps.shape[1], CONV_ACTIVATIONS[activation])
+
+
+def selective_scan(xz: torch.Tensor, z_offset: int, x: torch.Tensor, low: torch.Tensor, b_offset: int, c_offset: int,
+                   dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d: torch.Tensor, ctx, state: torch.Tensor,
+                   state_offset: int, out: torch.Tensor) -> None:
+    """S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n, y_c = sum_n S[c, n] C_n + D_c x_c, out = y silu(z), with
+    dt = softplus(``dt`` + ``dt_bias``) and A = -exp(``a_log``); all inputs float32."""
+    for t in (xz, x, low, dt, dt_bias, a_log, d):
+        _want(t, torch.float32, "selective_scan's inputs")
+    inner, n = a_log.shape
+    _call("frb_selective_scan", _ptr(xz), xz.shape[1], int(z_offset), _ptr(x), _ptr(low), low.shape[1], int(b_offset),
+          int(c_offset), _ptr(dt), _ptr(dt_bias), _ptr(a_log), _ptr(d), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
+          _ptr(ctx.cu_q_len), *_state_place(state, state_offset), _ptr(out), _code(out.dtype), ctx.num_seqs, inner, n)
+
+
+def gated_recurrence(yx: torch.Tensor, y_offset: int, y_bias: Optional[torch.Tensor], u: torch.Tensor, gates: torch.Tensor,
+                     a_bias: torch.Tensor, i_bias: torch.Tensor, lam: torch.Tensor, ctx, state: torch.Tensor, state_offset: int,
+                     out: torch.Tensor, *, block_width: int, gate_constant: float) -> None:
+    """a = exp(-gate_constant * sigmoid(r + a_bias) * softplus(lam)), S <- a S + sqrt(1 - a^2) sigmoid(i + i_bias) u,
+    out = S * gelu_tanh(y + y_bias); ``gates`` float32 [blocks, T, 2 * block_width] holds r then i of every block."""
+    for t in (yx, u, gates, a_bias, i_bias, lam):
+        _want(t, torch.float32, "gated_recurrence's inputs")
+    channels = u.shape[1]
+    _call("frb_gated_recurrence", _ptr(yx), yx.shape[1], int(y_offset), _ptr(y_bias), _ptr(u), _ptr(gates), _ptr(a_bias),
+          _ptr(i_bias), _ptr(lam), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.cu_q_len),
+          *_state_place(state, state_offset), _ptr(out), _code(out.dtype), ctx.num_seqs, u.shape[0], channels, int(block_width),
+          float(gate_constant))
+
+
+def state_space_scan(proj: torch.Tensor, z_offset: int, dt_offset: int, xbc: torch.Tensor, b_offset: int, c_offset: int,
+                     dt_bias: torch.Tensor, a_log: torch.Tensor, d: torch.Tensor, ctx, state: torch.Tensor, state_offset: int,
+                     out: torch.Tensor, *, heads: int, vdim: int, n: int, groups: int) -> None:
+    """Per head: S <- exp(-exp(a_log) dt) S + dt B x^T, y = S^T C + d x, out = y silu(z) in float32 [T, heads * vdim]."""
+    for t in (proj, xbc, dt_bias, a_log, d, out):
+        _want(t, torch.float32, "state_space_scan's operands")
+    _call("frb_state_space_scan", _ptr(proj), proj.shape[1], int(z_offset), int(dt_offset), _ptr(xbc), xbc.shape[1],
+          int(b_offset), int(c_offset), _ptr(dt_bias), _ptr(a_log), _ptr(d), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
+          _ptr(ctx.cu_q_len), *_state_place(state, state_offset), _ptr(out), ctx.num_seqs, heads, vdim, n, groups)
+
+
+def group_rms_norm(rows_in: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, norm_groups: int, eps: float) -> None:
+    """Each row in ``norm_groups`` equal parts, each divided by its root mean square, times ``weight``."""
+    _want(rows_in, torch.float32, "rows to norm")
+    _want(weight, torch.float32, "norm weight")
+    _call("frb_group_rms_norm", _ptr(rows_in), _ptr(weight), _ptr(out), _code(out.dtype), rows_in.shape[0], rows_in.shape[1],
+          int(norm_groups), float(eps))
+
+
 def gla_value_slices(dim: int, vdim: int) -> int:
     """Into how many slices of value columns :func:`gla_scan` cuts a head's state of ``dim`` x ``vdim`` (1 wherever a
     block's registers hold it: up to 32,768 elements with padding)."""
@@ -413,16 +581,32 @@ def qkv_prepare(qkv: torch.Tensor, q_weight: Optional[torch.Tensor], k_weight: O
 def attention_generic(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
                       tok_pos: torch.Tensor, tok_slot: torch.Tensor, out: torch.Tensor, *, num_heads: int,
                       num_kv_heads: int, head_dim: int, scale: float, window: Optional[int], v_dim: Optional[int] = None,
-                      slopes: Optional[torch.Tensor] = None) -> None:
+                      slopes: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                      sinks: Optional[torch.Tensor] = None, gate: Optional[torch.Tensor] = None) -> None:
     """``v_dim``: size of a value head if not ``head_dim``; ``slopes`` (float32 [num_heads]): the score of key j for
-    the query at position i is lowered by slopes[h] * (i - j)."""
+    the query at position i is lowered by slopes[h] * (i - j); ``chunk``: a query sees only the keys of its own chunk
+    of that many positions; ``sinks`` (float32 [num_heads]): exp(sinks[h]) joins the softmax's denominator;
+    ``gate`` (float32 [T, >= num_heads], rows may be wider): head h's output times sigmoid(gate[t, h])."""
     if k_pages.dtype != q.dtype or out.dtype != q.dtype:
         raise KernelError("queries, cache and output must have one dtype")
     if slopes is not None:
         _want(slopes, torch.float32, "distance slopes")
+    if sinks is not None:
+        _want(sinks, torch.float32, "softmax sinks")
+        if sinks.numel() != num_heads:
+            raise KernelError(f"{sinks.numel()} sinks for {num_heads} heads")
+    if gate is not None:
+        _want(gate, torch.float32, "head gates")
+        if gate.shape[0] != q.shape[0] or gate.shape[1] < num_heads:
+            raise KernelError(f"head gates of shape {list(gate.shape)} for {q.shape[0]} tokens of {num_heads} heads")
     _call("frb_attention_generic", _ptr(q), _ptr(k_pages), _ptr(v_pages), _code(q.dtype), _ptr(page_table),
           page_table.shape[1], _ptr(tok_pos), _ptr(tok_slot), _ptr(out), q.shape[0], num_heads, num_kv_heads, head_dim,
-          float(scale), int(window or 0), int(v_dim or head_dim), _ptr(slopes))
+          float(scale), int(window or 0), int(v_dim or head_dim), _ptr(slopes), int(chunk or 0), _ptr(sinks), _ptr(gate),
+          gate.shape[1] if gate is not None else 0)
+
+
+ROUTE_SOFTMAX, ROUTE_FLOOR = 2, 4      # bits of the routing kernels' ``renormalize`` (bit 0: divide by the picked scores' sum)
+ROUTE_WEIGHT_FLOOR = 1e-20             # what bit 2 adds to that sum
 
 
 def router_topk(logits: torch.Tensor, bias: Optional[torch.Tensor], top_k: int, renormalize: bool, routed_scale: float,

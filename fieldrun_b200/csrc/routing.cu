@@ -3,7 +3,9 @@
 //
 // Router (src/minimax.rs:94-104): s_e = 1/(1+exp(-z_e)); choice c_e = s_e + bias_e; experts in descending c,
 // a tie going to the lower id (the reference sorts stably); the first k; weight w_e = s_e / sum of the
-// picked s.  The bias enters the choice only.  Combination (src/minimax.rs:121-123): out[t] = sum over the
+// picked s.  The bias enters the choice only.  A second score, for models that have it: s = softmax(z) over all experts,
+// and the sum of the picked s gets 1e-20 added before the division.  The entry points take both in their `renormalize`
+// argument: bit 0 divides by the sum, bit 1 chooses the softmax, bit 2 adds the 1e-20.  Combination (src/minimax.rs:121-123): out[t] = sum over the
 // picked experts of w * y; here always in rank order, so the sum does not depend on the batch.
 #include "common.cuh"
 
@@ -15,6 +17,8 @@ __device__ __forceinline__ unsigned int ordered_bits(float v) {
     return (u & 0x80000000u) ? ~u : (u | 0x80000000u);
 }
 
+enum { ROUTE_RENORMALIZE = 1, ROUTE_SOFTMAX = 2, ROUTE_FLOOR = 4 };
+
 #define PICK_PER_LANE 8      // experts a lane keeps in registers: up to 256 experts on the fast path
 
 // One warp picks one token's experts.  z: the token's E logits; score/choice: E floats of scratch each.
@@ -23,7 +27,9 @@ __device__ __forceinline__ unsigned int ordered_bits(float v) {
 __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const float* __restrict__ bias, int num_experts,
                                              int top_k, int renormalize, float routed_scale, float* score, float* choice,
                                              int* __restrict__ ids, float* __restrict__ weights, int lane) {
-    float denom = 0.f;
+    const bool softmax = renormalize & ROUTE_SOFTMAX;
+    float denom = (renormalize & ROUTE_FLOOR) ? 1e-20f : 0.f;
+    renormalize &= ROUTE_RENORMALIZE;
     if (num_experts <= 32 * PICK_PER_LANE && top_k <= 32) {
         // the lane's candidates stay in registers; NaN scores count as the smallest value
         float mine[PICK_PER_LANE], sc[PICK_PER_LANE];
@@ -36,11 +42,23 @@ __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const 
             logit[i] = __ldcg(z + e);                                    // read through L2: another block may have written it
             shift[i] = bias ? __ldg(bias + e) : 0.f;
         }
+        float top_logit = -INFINITY, inv_total = 0.f;
+        if (softmax) {
+#pragma unroll
+            for (int i = 0; i < PICK_PER_LANE; ++i)
+                if (lane + 32 * i < num_experts) top_logit = fmaxf(top_logit, logit[i]);
+            top_logit = warp_max(top_logit);
+            float total = 0.f;
+#pragma unroll
+            for (int i = 0; i < PICK_PER_LANE; ++i)
+                if (lane + 32 * i < num_experts) total += expf(logit[i] - top_logit);
+            inv_total = 1.0f / warp_sum(total);
+        }
 #pragma unroll
         for (int i = 0; i < PICK_PER_LANE; ++i) {
             const int e = lane + 32 * i;
             if (e < num_experts) {
-                const float s = 1.0f / (1.0f + expf(-logit[i]));
+                const float s = softmax ? expf(logit[i] - top_logit) * inv_total : 1.0f / (1.0f + expf(-logit[i]));
                 sc[i] = s;
                 const float c = bias ? s + shift[i] : s;
                 mine[i] = c == c ? c : -INFINITY;
@@ -84,8 +102,16 @@ __device__ __forceinline__ void pick_experts(const float* __restrict__ z, const 
         __syncwarp();
         return;
     }
+    float top_logit = -INFINITY, inv_total = 0.f;
+    if (softmax) {
+        for (int e = lane; e < num_experts; e += 32) top_logit = fmaxf(top_logit, __ldcg(z + e));
+        top_logit = warp_max(top_logit);
+        float total = 0.f;
+        for (int e = lane; e < num_experts; e += 32) total += expf(__ldcg(z + e) - top_logit);
+        inv_total = 1.0f / warp_sum(total);
+    }
     for (int e = lane; e < num_experts; e += 32) {
-        const float s = 1.0f / (1.0f + expf(-__ldcg(z + e)));
+        const float s = softmax ? expf(__ldcg(z + e) - top_logit) * inv_total : 1.0f / (1.0f + expf(-__ldcg(z + e)));
         score[e] = s;
         choice[e] = bias ? s + bias[e] : s;
     }

@@ -1,0 +1,497 @@
+// Recurrences over a float32 state per sequence, and the short causal convolution that stands in front of them.
+//
+//   causal_conv      out[t, c] = act(bias[c] + sum_k taps[c, k] * in[t - (K-1) + k, c]), the inputs before a step's first
+//                    token coming from the state (the last K-1 inputs of the sequence; zeros for a new sequence)
+//   selective_scan   S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n;  y_c = sum_n S[c, n] C_n + D_c x_c;  y silu(z)
+//   gated_recurrence a = exp(-g r softplus(lam)),  S <- a S + sqrt(1 - a^2) i u,  out = S * act(y)    (per channel)
+//   state_space_scan per head: S <- exp(-exp(A_log) dt) S + dt B x^T (S is [N, vdim]);  y = S^T C + D x;  y silu(z)
+//   group_rms_norm   rows divided, in equal parts, by each part's root mean square, times a weight
+//
+// Everything here is float32: the rows come as the float32 results of the projections, the state lives in float32.
+// The state of a slot exists twice, [slot][2][floats]: a step that begins at position p reads copy (p & 1) and writes
+// copy ((p + n) & 1) after its n tokens, so a step of one token never writes what it reads and a recorded step that
+// holds a sequence twice computes the same bits in both rows.  A prompt's step may read and write the same copy: every
+// element of the state is then read and written by one thread only, which reads before it writes.
+//
+// A decay a = exp(l) with l close to 0 is kept as a - 1 = expm1(l) and applied as S + (a - 1) S: rounded to float32, a
+// itself would lose its distance from 1, by the same amount at every step, and over a thousand tokens that bias adds
+// up to 1e-4 of the state; the rounding of S + (a - 1) S has no preferred direction.
+#include "common.cuh"
+
+#define SCAN_TOKENS 8        // tokens whose rows are asked for together
+
+struct SeqTables {
+    const int* seq_slot;     // [B]
+    const int* seq_start;    // [B] position of the sequence's first new token
+    const int* cu_q_len;     // [B + 1] rows of the step before each sequence
+};
+
+struct StatePlace {
+    float* base;             // [slots][2][copy_floats]
+    long long copy_floats;   // floats of one copy of a slot's state
+    long long offset;        // where, within a copy, this kernel's part begins
+};
+
+__device__ __forceinline__ float* state_at(const StatePlace& s, int slot, int copy) {
+    return s.base + ((size_t)slot * 2 + copy) * s.copy_floats + s.offset;
+}
+
+__device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
+__device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
+__device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+__device__ __forceinline__ float gelu_tanh_f(float v) {
+    return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
+}
+
+// ---------------------------------------------------------------------------------------------------- causal_conv
+
+#define CONV_MAX_TAPS 16
+
+struct ConvParams {
+    const float* in;         // [T, in_stride]; channel c at column in_offset + c
+    const float* in_bias;    // [C] or null: added to every input
+    const float* taps;       // [C, K]; the last column weighs the current token
+    const float* bias;       // [C] or null
+    const int* tok_seq;      // [T]
+    SeqTables seq;
+    StatePlace state;        // [K - 1][C]: the last inputs, oldest first
+    float* out32;            // [T, C]
+    void* out_typed;         // null, or [T, C] in the model dtype
+    int in_stride, in_offset, channels, taps_count, activation, num_rows;
+};
+
+__device__ __forceinline__ float conv_activation(float v, int activation) { return activation == 1 ? silu_f(v) : v; }
+
+// A thread per (row, channel).  The thread of a sequence's first new row does all that touches the state: the
+// outputs of the first K-1 rows (the only ones that see inputs from before the step) and the new state.
+template <typename OutT>
+__global__ void __launch_bounds__(128) causal_conv_kernel(ConvParams p) {
+    after_previous_kernel();
+    const int c = blockIdx.y * 128 + threadIdx.x;
+    const int r = blockIdx.x;
+    if (c >= p.channels) return;
+    const int K = p.taps_count;
+    const int b = p.tok_seq[r];
+    const int row0 = p.seq.cu_q_len[b], n = p.seq.cu_q_len[b + 1] - row0;
+    const int i = r - row0;
+    if (i > 0 && i < K - 1) return;
+    float w[CONV_MAX_TAPS];
+#pragma unroll
+    for (int k = 0; k < CONV_MAX_TAPS; ++k) w[k] = k < K ? p.taps[(size_t)c * K + k] : 0.f;
+    const float bias = p.bias ? p.bias[c] : 0.f, in_bias = p.in_bias ? p.in_bias[c] : 0.f;
+    const float* in = p.in + p.in_offset + c;
+    OutT* typed = (OutT*)p.out_typed;
+    if (i >= K - 1) {
+        float acc = bias;
+#pragma unroll
+        for (int k = 0; k < CONV_MAX_TAPS; ++k)
+            if (k < K) acc += w[k] * (in[(size_t)(r - (K - 1) + k) * p.in_stride] + in_bias);
+        acc = conv_activation(acc, p.activation);
+        p.out32[(size_t)r * p.channels + c] = acc;
+        if (typed) typed[(size_t)r * p.channels + c] = from_f32<OutT>(acc);
+        return;                                 // with K == 1 there is no state and every row ends here
+    }
+    // i == 0
+    const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
+    const float* old_tail = state_at(p.state, slot, start & 1);
+    float* new_tail = state_at(p.state, slot, (start + n) & 1);
+    // hist[m], m < K-1: the inputs before the step; hist[K-1+j]: the step's own input j, for the rows handled here
+    float hist[2 * CONV_MAX_TAPS];
+#pragma unroll
+    for (int m = 0; m < CONV_MAX_TAPS; ++m) hist[m] = m < K - 1 ? old_tail[(size_t)m * p.channels + c] : 0.f;
+    const int own = min(n, K - 1);
+#pragma unroll
+    for (int j = 0; j < CONV_MAX_TAPS; ++j)
+        hist[CONV_MAX_TAPS + j] = j < own ? in[(size_t)(row0 + j) * p.in_stride] + in_bias : 0.f;
+    for (int j = 0; j < own; ++j) {
+        float acc = bias;
+        for (int k = 0; k < K; ++k) {
+            const int at = j - (K - 1) + k;                       // index among the step's inputs; negative: before it
+            const float v = at >= 0 ? hist[CONV_MAX_TAPS + at] : hist[K - 1 + at];
+            acc += w[k] * v;
+        }
+        acc = conv_activation(acc, p.activation);
+        p.out32[(size_t)(row0 + j) * p.channels + c] = acc;
+        if (typed) typed[(size_t)(row0 + j) * p.channels + c] = from_f32<OutT>(acc);
+    }
+    for (int m = 0; m < K - 1; ++m) {
+        const int at = n - (K - 1) + m;                           // the step's input that becomes entry m of the new state
+        float v;
+        if (at < 0) v = hist[K - 1 + at];
+        else if (at < own) v = hist[CONV_MAX_TAPS + at];
+        else v = in[(size_t)(row0 + at) * p.in_stride] + in_bias;
+        new_tail[(size_t)m * p.channels + c] = v;
+    }
+}
+
+FRB_API int frb_causal_conv(const float* in, int in_stride, int in_offset, const float* in_bias, const float* taps,
+                            const float* bias, const int* tok_seq, const int* seq_slot, const int* seq_start,
+                            const int* cu_q_len, float* state, long long copy_floats, long long state_offset, float* out32,
+                            void* out_typed, int typed_dtype, int num_rows, int channels, int taps_count, int activation,
+                            cudaStream_t stream) {
+    if (num_rows == 0) return 0;
+    FRB_CHECK_ARG(taps_count >= 1 && taps_count <= CONV_MAX_TAPS, "causal_conv: %d taps are outside 1..%d", taps_count,
+                  CONV_MAX_TAPS);
+    ConvParams p;
+    p.in = in; p.in_bias = in_bias; p.taps = taps; p.bias = bias; p.tok_seq = tok_seq;
+    p.seq = SeqTables{seq_slot, seq_start, cu_q_len};
+    p.state = StatePlace{state, copy_floats, state_offset};
+    p.out32 = out32; p.out_typed = out_typed; p.in_stride = in_stride; p.in_offset = in_offset; p.channels = channels;
+    p.taps_count = taps_count; p.activation = activation; p.num_rows = num_rows;
+    FRB_CHECK_ARG((channels + 127) / 128 <= 65535, "causal_conv: %d channels exceed the grid", channels);
+    dim3 grid(num_rows, (channels + 127) / 128);
+    FRB_DISPATCH_DTYPE(typed_dtype, OutT, {
+        launch_dependent(causal_conv_kernel<OutT>, grid, dim3(128), 0, stream, p);
+    });
+    FRB_RETURN_LAUNCH("causal_conv");
+}
+
+// ---------------------------------------------------------------------------------------------------- selective_scan
+
+#define SEL_REGS 16          // state elements of one channel that a thread keeps
+#define SEL_BLOCK 128
+
+struct SelScanParams {
+    const float* xz;         // [T, xz_stride]: z of channel c at z_offset + c
+    const float* x;          // [T, inner]: the convolution's output
+    const float* low;        // [T, low_stride]: B at b_offset, C at c_offset
+    const float* dt;         // [T, inner]: the step size before bias and softplus
+    const float* dt_bias;    // [inner]
+    const float* a_log;      // [inner, N]
+    const float* d;          // [inner]
+    SeqTables seq;
+    StatePlace state;        // [inner][N]
+    void* out;               // [T, inner]
+    int xz_stride, z_offset, low_stride, b_offset, c_offset, inner, N, split;
+};
+
+// A channel's N state elements lie on `split` neighbouring lanes (a power of two), SEL_REGS each.
+template <typename OutT>
+__global__ void __launch_bounds__(SEL_BLOCK) selective_scan_kernel(SelScanParams p) {
+    extern __shared__ float sm[];
+    after_previous_kernel();
+    const int N = p.N, split = p.split;
+    float* s_b = sm;                        // [SCAN_TOKENS][N]
+    float* s_c = sm + SCAN_TOKENS * N;      // [SCAN_TOKENS][N]
+    const int b = blockIdx.y;
+    const int per_block = SEL_BLOCK / split;
+    const int part = threadIdx.x % split;
+    const int c = blockIdx.x * per_block + threadIdx.x / split;
+    const bool live = c < p.inner;
+    const int row0 = p.seq.cu_q_len[b], n_tok = p.seq.cu_q_len[b + 1] - row0;
+    const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
+    const int n0 = part * SEL_REGS;
+    float S[SEL_REGS], A[SEL_REGS];
+    const float* s_in = state_at(p.state, slot, start & 1);
+#pragma unroll
+    for (int i = 0; i < SEL_REGS; ++i) {
+        const bool has = live && n0 + i < N;
+        S[i] = has ? s_in[(size_t)c * N + n0 + i] : 0.f;
+        A[i] = has ? -expf(p.a_log[(size_t)c * N + n0 + i]) : 0.f;
+    }
+    const float bias = live ? p.dt_bias[c] : 0.f, dskip = live ? p.d[c] : 0.f;
+    OutT* out = (OutT*)p.out;
+    for (int t0 = 0; t0 < n_tok; t0 += SCAN_TOKENS) {
+        const int count = min(SCAN_TOKENS, n_tok - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < count * N; i += SEL_BLOCK) {
+            const int t = i / N, n = i - t * N;
+            const float* row = p.low + (size_t)(row0 + t0 + t) * p.low_stride;
+            s_b[i] = row[p.b_offset + n];
+            s_c[i] = row[p.c_offset + n];
+        }
+        float dtv[SCAN_TOKENS], xv[SCAN_TOKENS], zv[SCAN_TOKENS];
+#pragma unroll
+        for (int t = 0; t < SCAN_TOKENS; ++t) {
+            const bool has = live && t < count;
+            const size_t row = (size_t)(row0 + t0 + t);
+            dtv[t] = has ? p.dt[row * p.inner + c] : 0.f;
+            xv[t] = has ? p.x[row * p.inner + c] : 0.f;
+            zv[t] = has && part == 0 ? p.xz[row * p.xz_stride + p.z_offset + c] : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int t = 0; t < SCAN_TOKENS; ++t) {
+            if (t < count) {
+                const float step = softplus_f(dtv[t] + bias);
+                const float sx = step * xv[t];
+                float y = 0.f;
+#pragma unroll
+                for (int i = 0; i < SEL_REGS; ++i) {
+                    if (n0 + i < N) {
+                        S[i] = fmaf(expm1f(step * A[i]), S[i], S[i]) + sx * s_b[t * N + n0 + i];
+                        y += S[i] * s_c[t * N + n0 + i];
+                    }
+                }
+                for (int o = 1; o < split; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
+                if (live && part == 0)
+                    out[(size_t)(row0 + t0 + t) * p.inner + c] = from_f32<OutT>((y + dskip * xv[t]) * silu_f(zv[t]));
+            }
+        }
+    }
+    if (live) {
+        float* s_out = state_at(p.state, slot, (start + n_tok) & 1);
+#pragma unroll
+        for (int i = 0; i < SEL_REGS; ++i)
+            if (n0 + i < N) s_out[(size_t)c * N + n0 + i] = S[i];
+    }
+}
+
+FRB_API int frb_selective_scan(const float* xz, int xz_stride, int z_offset, const float* x, const float* low, int low_stride,
+                               int b_offset, int c_offset, const float* dt, const float* dt_bias, const float* a_log,
+                               const float* d, const int* seq_slot, const int* seq_start, const int* cu_q_len, float* state,
+                               long long copy_floats, long long state_offset, void* out, int out_dtype, int num_seqs, int inner,
+                               int N, cudaStream_t stream) {
+    if (num_seqs == 0) return 0;
+    int split = 1;
+    while (split * SEL_REGS < N) split <<= 1;
+    FRB_CHECK_ARG(split <= 32, "selective_scan: a state of %d per channel is more than the kernel's %d", N, 32 * SEL_REGS);
+    FRB_CHECK_ARG(num_seqs <= 65535, "selective_scan: %d sequences exceed the grid", num_seqs);
+    SelScanParams p;
+    p.xz = xz; p.xz_stride = xz_stride; p.z_offset = z_offset; p.x = x; p.low = low; p.low_stride = low_stride;
+    p.b_offset = b_offset; p.c_offset = c_offset; p.dt = dt; p.dt_bias = dt_bias; p.a_log = a_log; p.d = d;
+    p.seq = SeqTables{seq_slot, seq_start, cu_q_len};
+    p.state = StatePlace{state, copy_floats, state_offset};
+    p.out = out; p.inner = inner; p.N = N; p.split = split;
+    const int per_block = SEL_BLOCK / split;
+    dim3 grid((inner + per_block - 1) / per_block, num_seqs);
+    const size_t smem = (size_t)2 * SCAN_TOKENS * N * sizeof(float);
+    FRB_DISPATCH_DTYPE(out_dtype, OutT, {
+        launch_dependent(selective_scan_kernel<OutT>, grid, dim3(SEL_BLOCK), smem, stream, p);
+    });
+    FRB_RETURN_LAUNCH("selective_scan");
+}
+
+// ---------------------------------------------------------------------------------------------------- gated_recurrence
+
+struct GatedRecParams {
+    const float* yx;         // [T, yx_stride]: the gate branch before bias and activation, channel c at y_offset + c
+    const float* y_bias;     // [C] or null
+    const float* u;          // [T, C]: the convolution's output
+    const float* gates;      // [blocks, T, 2 * bw]: per block the recurrence gate's rows, then the input gate's
+    const float* a_bias;     // [C]
+    const float* i_bias;     // [C]
+    const float* lam;        // [C]
+    SeqTables seq;
+    StatePlace state;        // [C]
+    void* out;               // [T, C]
+    float gate_constant;
+    int yx_stride, y_offset, channels, block_width, num_rows;
+};
+
+template <typename OutT>
+__global__ void __launch_bounds__(128) gated_recurrence_kernel(GatedRecParams p) {
+    after_previous_kernel();
+    const int c = blockIdx.x * 128 + threadIdx.x;
+    const int b = blockIdx.y;
+    if (c >= p.channels) return;
+    const int row0 = p.seq.cu_q_len[b], n_tok = p.seq.cu_q_len[b + 1] - row0;
+    const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
+    const int bw = p.block_width, blk = c / bw, j = c - blk * bw;
+    const float* g_rows = p.gates + (size_t)blk * p.num_rows * 2 * bw + j;
+    const float y_bias = p.y_bias ? p.y_bias[c] : 0.f, a_bias = p.a_bias[c], i_bias = p.i_bias[c];
+    const float rate = p.gate_constant * softplus_f(p.lam[c]);
+    float S = state_at(p.state, slot, start & 1)[c];
+    OutT* out = (OutT*)p.out;
+    for (int t0 = 0; t0 < n_tok; t0 += SCAN_TOKENS) {
+        const int count = min(SCAN_TOKENS, n_tok - t0);
+        float yv[SCAN_TOKENS], uv[SCAN_TOKENS], rv[SCAN_TOKENS], iv[SCAN_TOKENS];
+#pragma unroll
+        for (int t = 0; t < SCAN_TOKENS; ++t) {
+            const bool has = t < count;
+            const size_t row = (size_t)(row0 + t0 + t);
+            yv[t] = has ? p.yx[row * p.yx_stride + p.y_offset + c] : 0.f;
+            uv[t] = has ? p.u[row * p.channels + c] : 0.f;
+            rv[t] = has ? g_rows[row * 2 * bw] : 0.f;
+            iv[t] = has ? g_rows[row * 2 * bw + bw] : 0.f;
+        }
+#pragma unroll
+        for (int t = 0; t < SCAN_TOKENS; ++t) {
+            if (t < count) {
+                const float r = sigmoid_f(rv[t] + a_bias), in_gate = sigmoid_f(iv[t] + i_bias);
+                const float log_a = -rate * r;
+                S = fmaf(expm1f(log_a), S, S) + sqrtf(-expm1f(2.0f * log_a)) * in_gate * uv[t];   // 1 - a^2 without cancellation
+                out[(size_t)(row0 + t0 + t) * p.channels + c] = from_f32<OutT>(S * gelu_tanh_f(yv[t] + y_bias));
+            }
+        }
+    }
+    state_at(p.state, slot, (start + n_tok) & 1)[c] = S;
+}
+
+FRB_API int frb_gated_recurrence(const float* yx, int yx_stride, int y_offset, const float* y_bias, const float* u,
+                                 const float* gates, const float* a_bias, const float* i_bias, const float* lam,
+                                 const int* seq_slot, const int* seq_start, const int* cu_q_len, float* state,
+                                 long long copy_floats, long long state_offset, void* out, int out_dtype, int num_seqs,
+                                 int num_rows, int channels, int block_width, float gate_constant, cudaStream_t stream) {
+    if (num_seqs == 0) return 0;
+    FRB_CHECK_ARG(num_seqs <= 65535, "gated_recurrence: %d sequences exceed the grid", num_seqs);
+    FRB_CHECK_ARG(block_width >= 1 && channels % block_width == 0, "gated_recurrence: %d channels in blocks of %d", channels,
+                  block_width);
+    GatedRecParams p;
+    p.yx = yx; p.yx_stride = yx_stride; p.y_offset = y_offset; p.y_bias = y_bias; p.u = u; p.gates = gates; p.a_bias = a_bias;
+    p.i_bias = i_bias; p.lam = lam; p.seq = SeqTables{seq_slot, seq_start, cu_q_len};
+    p.state = StatePlace{state, copy_floats, state_offset};
+    p.out = out; p.gate_constant = gate_constant; p.channels = channels; p.block_width = block_width; p.num_rows = num_rows;
+    dim3 grid((channels + 127) / 128, num_seqs);
+    FRB_DISPATCH_DTYPE(out_dtype, OutT, {
+        launch_dependent(gated_recurrence_kernel<OutT>, grid, dim3(128), 0, stream, p);
+    });
+    FRB_RETURN_LAUNCH("gated_recurrence");
+}
+
+// ---------------------------------------------------------------------------------------------------- state_space_scan
+
+struct SsdParams {
+    const float* proj;       // [T, proj_stride]: z of channel j at z_offset + j, dt of head h at dt_offset + h
+    const float* xbc;        // [T, xbc_stride]: x of head h at h * vdim, B of group g at b_offset + g * N, C at c_offset + g * N
+    const float* dt_bias;    // [heads]
+    const float* a_log;      // [heads]
+    const float* d;          // [heads]
+    SeqTables seq;
+    StatePlace state;        // [heads][N][vdim]
+    float* out;              // [T, heads * vdim]: y silu(z), float32 (the norm follows)
+    int proj_stride, z_offset, dt_offset, xbc_stride, b_offset, c_offset, heads, vdim, N, groups, parts, npad;
+};
+
+// A block takes (sequence, head, slice of 32 value columns); warp `part` keeps NREG rows of the state for each of its
+// lane's column.  Tokens go eight at a time: their B, C, x, step and decay are laid into shared memory by the whole
+// block, the eight steps run without a barrier, and the warps' shares of y are added in warp order.
+template <int NREG>
+__global__ void __launch_bounds__(512) state_space_scan_kernel(SsdParams p) {
+    extern __shared__ float sm[];
+    after_previous_kernel();
+    const int N = p.N, npad = p.npad, parts = p.parts, vdim = p.vdim;
+    float* s_b = sm;                                   // [SCAN_TOKENS][npad]
+    float* s_c = s_b + SCAN_TOKENS * npad;             // [SCAN_TOKENS][npad]
+    float* s_x = s_c + SCAN_TOKENS * npad;             // [SCAN_TOKENS][32]
+    float* s_dt = s_x + SCAN_TOKENS * 32;              // [SCAN_TOKENS]
+    float* s_a = s_dt + SCAN_TOKENS;                   // [SCAN_TOKENS]
+    float* s_y = s_a + SCAN_TOKENS;                    // [SCAN_TOKENS][parts][32]
+    const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;
+    const int g = h / (p.heads / p.groups);
+    const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
+    const int v = v0 + lane;
+    const bool col = v < vdim;
+    const int row0 = p.seq.cu_q_len[b], n_tok = p.seq.cu_q_len[b + 1] - row0;
+    const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
+    const int n0 = part * NREG;
+    const float* s_in = state_at(p.state, slot, start & 1) + (size_t)h * N * vdim;
+    float S[NREG];
+#pragma unroll
+    for (int i = 0; i < NREG; ++i) S[i] = (col && n0 + i < N) ? s_in[(size_t)(n0 + i) * vdim + v] : 0.f;
+    const float dt_bias = p.dt_bias[h], rate = expf(p.a_log[h]), dskip = p.d[h];
+    for (int i = threadIdx.x; i < 2 * SCAN_TOKENS * npad; i += blockDim.x) s_b[i] = 0.f;    // the padding stays zero
+    for (int t0 = 0; t0 < n_tok; t0 += SCAN_TOKENS) {
+        const int count = min(SCAN_TOKENS, n_tok - t0);
+        __syncthreads();
+        for (int i = threadIdx.x; i < count * N; i += blockDim.x) {
+            const int t = i / N, n = i - t * N;
+            const float* row = p.xbc + (size_t)(row0 + t0 + t) * p.xbc_stride;
+            s_b[t * npad + n] = row[p.b_offset + g * N + n];
+            s_c[t * npad + n] = row[p.c_offset + g * N + n];
+        }
+        for (int i = threadIdx.x; i < count * 32; i += blockDim.x) {
+            const int t = i >> 5, l = i & 31;
+            s_x[i] = v0 + l < vdim ? p.xbc[(size_t)(row0 + t0 + t) * p.xbc_stride + h * vdim + v0 + l] : 0.f;
+        }
+        if (threadIdx.x < count) {
+            const float step = softplus_f(p.proj[(size_t)(row0 + t0 + threadIdx.x) * p.proj_stride + p.dt_offset + h] + dt_bias);
+            s_dt[threadIdx.x] = step;
+            s_a[threadIdx.x] = expm1f(-rate * step);               // the decay less one
+        }
+        __syncthreads();
+#pragma unroll
+        for (int t = 0; t < SCAN_TOKENS; ++t) {
+            if (t < count) {
+                const float am1 = s_a[t], sx = s_dt[t] * s_x[t * 32 + lane];
+                float y = 0.f;
+#pragma unroll
+                for (int i = 0; i < NREG; ++i) {
+                    S[i] = fmaf(am1, S[i], S[i]) + s_b[t * npad + n0 + i] * sx;
+                    y += S[i] * s_c[t * npad + n0 + i];
+                }
+                s_y[(t * parts + part) * 32 + lane] = y;
+            }
+        }
+        __syncthreads();
+        for (int i = threadIdx.x; i < count * 32; i += blockDim.x) {
+            const int t = i >> 5, l = i & 31;
+            if (v0 + l < vdim) {
+                float y = 0.f;
+                for (int q = 0; q < parts; ++q) y += s_y[(t * parts + q) * 32 + l];
+                const size_t row = (size_t)(row0 + t0 + t);
+                const int channel = h * vdim + v0 + l;
+                const float z = p.proj[row * p.proj_stride + p.z_offset + channel];
+                p.out[row * (size_t)(p.heads * vdim) + channel] = (y + dskip * s_x[i]) * silu_f(z);
+            }
+        }
+    }
+    if (col) {
+        float* s_out = state_at(p.state, slot, (start + n_tok) & 1) + (size_t)h * N * vdim;
+#pragma unroll
+        for (int i = 0; i < NREG; ++i)
+            if (n0 + i < N) s_out[(size_t)(n0 + i) * vdim + v] = S[i];
+    }
+}
+
+FRB_API int frb_state_space_scan(const float* proj, int proj_stride, int z_offset, int dt_offset, const float* xbc,
+                                 int xbc_stride, int b_offset, int c_offset, const float* dt_bias, const float* a_log,
+                                 const float* d, const int* seq_slot, const int* seq_start, const int* cu_q_len, float* state,
+                                 long long copy_floats, long long state_offset, float* out, int num_seqs, int heads, int vdim,
+                                 int N, int groups, cudaStream_t stream) {
+    if (num_seqs == 0) return 0;
+    FRB_CHECK_ARG(groups >= 1 && heads % groups == 0, "state_space_scan: %d heads are not a multiple of %d groups", heads, groups);
+    FRB_CHECK_ARG(N >= 1 && N <= 1024, "state_space_scan: a state of %d rows per head is outside 1..1024", N);
+    FRB_CHECK_ARG(heads <= 65535 && (vdim + 31) / 32 <= 65535, "state_space_scan: %d heads of %d exceed the grid", heads, vdim);
+    int nreg = 8;
+    while ((N + nreg - 1) / nreg > 16) nreg <<= 1;
+    SsdParams p;
+    p.proj = proj; p.proj_stride = proj_stride; p.z_offset = z_offset; p.dt_offset = dt_offset; p.xbc = xbc;
+    p.xbc_stride = xbc_stride; p.b_offset = b_offset; p.c_offset = c_offset; p.dt_bias = dt_bias; p.a_log = a_log; p.d = d;
+    p.seq = SeqTables{seq_slot, seq_start, cu_q_len};
+    p.state = StatePlace{state, copy_floats, state_offset};
+    p.out = out; p.heads = heads; p.vdim = vdim; p.N = N; p.groups = groups;
+    p.parts = (N + nreg - 1) / nreg;
+    p.npad = p.parts * nreg;
+    const size_t smem = ((size_t)2 * SCAN_TOKENS * p.npad + SCAN_TOKENS * 32 + 2 * SCAN_TOKENS + (size_t)SCAN_TOKENS * p.parts * 32)
+                        * sizeof(float);
+    dim3 grid(num_seqs, heads, (vdim + 31) / 32);
+    dim3 block(32 * p.parts);
+    if (nreg == 8) launch_dependent(state_space_scan_kernel<8>, grid, block, smem, stream, p);
+    else if (nreg == 16) launch_dependent(state_space_scan_kernel<16>, grid, block, smem, stream, p);
+    else if (nreg == 32) launch_dependent(state_space_scan_kernel<32>, grid, block, smem, stream, p);
+    else launch_dependent(state_space_scan_kernel<64>, grid, block, smem, stream, p);
+    FRB_RETURN_LAUNCH("state_space_scan");
+}
+
+// ---------------------------------------------------------------------------------------------------- group_rms_norm
+
+template <typename OutT>
+__global__ void __launch_bounds__(128) group_rms_norm_kernel(const float* __restrict__ in, const float* __restrict__ weight,
+                                                             OutT* __restrict__ out, int width, int part, float eps) {
+    __shared__ float scratch[32];
+    after_previous_kernel();
+    const size_t base = (size_t)blockIdx.x * width + (size_t)blockIdx.y * part;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < part; i += 128) {
+        const float v = in[base + i];
+        ss += v * v;
+    }
+    ss = block_sum<128>(ss, scratch);
+    const float rinv = 1.0f / sqrtf(ss / (float)part + eps);
+    for (int i = threadIdx.x; i < part; i += 128)
+        out[base + i] = from_f32<OutT>(in[base + i] * rinv * weight[blockIdx.y * part + i]);
+}
+
+FRB_API int frb_group_rms_norm(const float* in, const float* weight, void* out, int out_dtype, int num_rows, int width,
+                               int norm_groups, float eps, cudaStream_t stream) {
+    if (num_rows == 0) return 0;
+    FRB_CHECK_ARG(norm_groups >= 1 && width % norm_groups == 0 && norm_groups <= 65535,
+                  "group_rms_norm: a row of %d in %d parts", width, norm_groups);
+    dim3 grid(num_rows, norm_groups);
+    FRB_DISPATCH_DTYPE(out_dtype, OutT, {
+        launch_dependent(group_rms_norm_kernel<OutT>, grid, dim3(128), 0, stream, in, weight, (OutT*)out, width,
+                         width / norm_groups, eps);
+    });
+    FRB_RETURN_LAUNCH("group_rms_norm");
+}

@@ -48,6 +48,7 @@ class DecoderModel:
                 build_part("feed_forward", layer.feed_forward, self.dtype) if layer.feed_forward is not None else None,
                 build_part("norm", layer.mixer_norm, self.dtype),
                 build_part("norm", layer.feed_forward_norm, self.dtype) if layer.feed_forward_norm is not None else None))
+        self.connectors = [build_part("connector", spec, self.dtype) for spec in plan.connectors]
         self.final_norm = build_part("norm", plan.final_norm, self.dtype)
         self.head = build_part("head", plan.head, self.dtype)
         self.head_is_tied = plan.head.tensors.get("weight") == plan.embedding.tensors.get("weight")
@@ -56,11 +57,17 @@ class DecoderModel:
     # -- tensors -------------------------------------------------------------------------------------
     def all_parts(self):
         parts = [self.embedding]
+        parts.extend(self.connectors)
         for block in self.blocks:
             parts.extend(block.parts())
         parts.append(self.final_norm)
         parts.append(self.head)
-        return parts
+        flat = []
+        while parts:                                   # a part made of parts counts with all of them
+            part = parts.pop(0)
+            flat.append(part)
+            parts[:0] = part.children()
+        return flat
 
     def tensor_needs(self) -> list[TensorNeed]:
         needs: list[TensorNeed] = []
@@ -72,6 +79,8 @@ class DecoderModel:
         if self.dtype == torch.float32:
             require_true_float32()
         self.embedding.load(source)
+        for connector in self.connectors:
+            connector.load(source)
         for block in self.blocks:
             for part in block.parts():
                 part.load(source)
@@ -133,8 +142,15 @@ class DecoderModel:
         if not self.loaded:
             raise RuntimeError("the model has no weights yet")
         x = self.embedding.forward(ctx, tokens)
+        first = None
+        if self.connectors:
+            # a connector mixes the embedding's rows back in; the stream itself is updated in place from here on
+            first = ctx.buffer("stream.first", tuple(x.shape), torch.float32)
+            first.copy_(x)
         pending = None
         for run in self.plan.run_order:
+            if run.connector is not None:
+                x, pending = self.connectors[run.connector[0]].forward(ctx, x, pending, first, run.connector[1]), None
             x, pending = self.blocks[run.layer].forward(ctx, x, pending, cache.line(run.cache_line), run.writes_cache)
         if logit_rows is None or logit_rows.numel() == 0:
             return None

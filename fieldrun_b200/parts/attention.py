@@ -16,7 +16,11 @@ result), ``query_temperature`` ``{"coef", "every"}`` (the normed query at positi
 1 + coef * ln(floor((p + 1) / every) + 1)), ``distance_slopes`` (one slope per query head: the score of key j
 for the query at position i is lowered by slope * (i - j); this is the position encoding that is not a rotation),
 ``shares_kv`` (the layer has no key and value projections: it attends, with its own queries, over the cache
-line of an earlier layer, which the plan's run order names).
+line of an earlier layer, which the plan's run order names), ``chunk`` (the query at position i sees key j <= i only
+if floor(i / chunk) == floor(j / chunk), chunks counted from the sequence's position 0; the cache gives back the pages
+before the current chunk), ``sink`` (a learned number per query head whose exponential joins the softmax's
+denominator: no key, no value, not scaled, counted once), ``head_gate`` (head h's output is multiplied by
+sigmoid(W_g x)_h, one row of W_g per head, before the output projection).
 """
 from __future__ import annotations
 
@@ -65,6 +69,13 @@ class GQAAttention(Mixer):
         self.window = a.get("window")
         if self.window is not None and int(self.window) <= 0:
             raise ValueError(f"an attention window of {self.window} keys")
+        self.chunk = int(a["chunk"]) if a.get("chunk") is not None else None
+        if self.chunk is not None and self.chunk <= 0:
+            raise ValueError(f"attention in chunks of {self.chunk} positions")
+        self.has_sink = bool(a.get("sink", False))
+        self.has_head_gate = bool(a.get("head_gate", False))
+        self.sinks: Optional[torch.Tensor] = None
+        self.w_gate: Optional[torch.Tensor] = None
         if self.num_heads % self.num_kv_heads:
             raise ValueError(f"{self.num_heads} heads are not a multiple of {self.num_kv_heads} kv heads")
         if not 1 <= self.head_dim <= 256:
@@ -104,6 +115,10 @@ class GQAAttention(Mixer):
         elif self.qk_norm == "per_head":
             needs["q_norm"] = TensorNeed(self.name_of("q_norm"), (self.head_dim,), VECTOR, "around_one")
             needs["k_norm"] = TensorNeed(self.name_of("k_norm"), (self.head_dim,), VECTOR, "around_one")
+        if self.has_sink:
+            needs["sink"] = TensorNeed(self.name_of("sink"), (self.num_heads,), VECTOR, "bias")
+        if self.has_head_gate:
+            needs["gate_proj"] = TensorNeed(self.name_of("gate_proj"), (self.num_heads, self.hidden_size), MATRIX, "normal")
         if self.shares_kv:                       # keys and values, with all that makes them, are another layer's
             for local in ("k_proj", "v_proj", "k_bias", "v_bias", "k_norm"):
                 needs.pop(local, None)
@@ -120,6 +135,10 @@ class GQAAttention(Mixer):
         if self.has_bias:
             biases = ("q_bias",) if self.shares_kv else ("q_bias", "k_bias", "v_bias")
             self.b_qkv = torch.cat([source.fetch(needs[n]) for n in biases], dim=0).contiguous()
+        if self.has_sink:
+            self.sinks = source.fetch(needs["sink"])
+        if self.has_head_gate:
+            self.w_gate = source.fetch(needs["gate_proj"])
         if self.qk_norm != "none":
             self.q_norm = source.fetch(needs["q_norm"])
             self.k_norm = source.fetch(needs["k_norm"]) if "k_norm" in needs else None
@@ -128,7 +147,7 @@ class GQAAttention(Mixer):
     def cache_need(self) -> CacheNeed:
         return CacheNeed(kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                          window=int(self.window) if self.window is not None else None,
-                         value_dim=self.value_dim if self.value_dim != self.head_dim else 0)
+                         value_dim=self.value_dim if self.value_dim != self.head_dim else 0, chunk=self.chunk)
 
     def prepare(self, num_positions: int, device) -> None:
         if self.position is not None and self.position.rotary_dim > 0:
@@ -153,16 +172,18 @@ class GQAAttention(Mixer):
                         tables_final=True,      # the step's tables were there before the projection above began
                         bias=self.b_qkv, v_dim=self.value_dim, q_temp=self.q_temp)
         out = ctx.buffer("attention.out", (tokens, self.out_width), self.dtype)
-        self.attend(ctx, q, line, out)
+        gate = linear(act, self.w_gate) if self.has_head_gate else None          # float32 [T, heads], before the sigmoid
+        self.attend(ctx, q, line, out, gate)
         return linear(out, self.w_o)
 
-    def attend(self, ctx, q: torch.Tensor, line: LineView, out: torch.Tensor) -> None:
+    def attend(self, ctx, q: torch.Tensor, line: LineView, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
         """Tensor-core kernels for bfloat16 and head sizes of 32, 64, 96 or 128 (tcgen05 for prompts with head
         sizes 64 and 128, mma.sync otherwise), keys and values of one size; the general kernel for everything else.
-        All of them take the distance slopes."""
+        All of them take the distance slopes; chunks, sinks and head gates go through the general kernel."""
         common = dict(num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
                       scale=self.softmax_scale, window=self.window, slopes=self.slopes)
-        if self.value_dim == self.head_dim and self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
+        plain = self.chunk is None and self.sinks is None and gate is None
+        if plain and self.value_dim == self.head_dim and self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
             if ctx.is_decode and self.num_heads // self.num_kv_heads <= 16:
                 chunks = (ctx.max_kv_len + ops.ATTENTION_CHUNK - 1) // ops.ATTENTION_CHUNK
                 part_o = ctx.buffer("attention.part_o", (ctx.num_seqs, self.num_heads, chunks, self.head_dim), torch.float32)
@@ -182,7 +203,7 @@ class GQAAttention(Mixer):
                                           ctx.seq_start, ctx.seq_q_len, ctx.cu_q_len, out, **common)
             return
         ops.attention_generic(q, line.keys, line.values, line.page_table, ctx.tok_pos, ctx.tok_slot, out,
-                              v_dim=self.value_dim, **common)
+                              v_dim=self.value_dim, chunk=self.chunk, sinks=self.sinks, gate=gate, **common)
 
 
 register_part("mixer", "gqa_attention", GQAAttention, replace=True)

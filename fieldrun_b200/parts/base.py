@@ -20,6 +20,8 @@ Interfaces
     ``pending`` is an update not yet added to x, so that the next norm adds it.
 ``Norm.add_normed(ctx, update, x)`` -> x in the model dtype
     the other place of a norm: x <- x + norm(update), for blocks whose sublayers read x itself.
+``Connector.forward(ctx, x, pending, first, index)`` -> the new stream [T, width] (float32)
+    a part between two runs that rewrites the whole stream; ``first`` holds the embedding's rows.
 """
 from __future__ import annotations
 
@@ -57,6 +59,11 @@ class Part:
     def load(self, source: TensorSource) -> None:
         pass
 
+    def children(self) -> list["Part"]:
+        """Parts that this part is put together from (a mixer made of two mixers); the model counts their tensors,
+        kernels and ``replayable`` with its own."""
+        return []
+
     def name_of(self, local: str) -> str:
         try:
             return self.spec.tensors[local]
@@ -92,6 +99,30 @@ class WeightedRows(DeferredUpdate):
         out = ctx.buffer("weighted_rows.sum", (self.weights.shape[0], self.rows.shape[1]), torch.float32)
         ops.expert_combine(self.rows, self.weights, self.row_map, out)
         return out
+
+
+class UpdateSum(DeferredUpdate):
+    """Several updates of one stream that are added together: float32 tensors [T, width] and at most one
+    :class:`WeightedRows`.  A block whose sublayers all read the same x leaves their outputs in this form, so
+    that the norm which reads the stream next adds them while it reads (a norm that does not know the form
+    gets their sum from ``materialize``)."""
+
+    def __init__(self, updates):
+        self.tensors = [u for u in updates if isinstance(u, torch.Tensor)]
+        self.weighted = [u for u in updates if isinstance(u, WeightedRows)]
+        other = [u for u in updates if u is not None and not isinstance(u, (torch.Tensor, WeightedRows))]
+        if other or len(self.weighted) > 1:
+            raise ValueError("an UpdateSum holds float32 tensors and at most one WeightedRows")
+
+    def materialize(self, ctx) -> torch.Tensor:
+        from ..csrc import ops
+        total = None
+        for update in self.tensors + [w.materialize(ctx) for w in self.weighted]:
+            if total is None:
+                total = update
+            else:
+                ops.add_rows(total, update)
+        return total
 
 
 def as_tensor(ctx, update):
@@ -155,6 +186,13 @@ class FeedForward(Part):
         return self.forward(ctx, act, act32)
 
 
+class Connector(Part):
+    """A part that stands between two runs of the run order and rewrites the stream as a whole."""
+
+    def forward(self, ctx, x: torch.Tensor, pending, first: torch.Tensor, index: int) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class Block:
     def __init__(self, mixer: Mixer, feed_forward: FeedForward, mixer_norm: Norm, feed_forward_norm: Norm):
         self.mixer, self.feed_forward = mixer, feed_forward
@@ -170,6 +208,7 @@ class Block:
 
 _REGISTRIES: dict[str, dict[str, Callable[..., Any]]] = {
     "mixer": {}, "feed_forward": {}, "norm": {}, "position": {}, "block": {}, "embedding": {}, "head": {},
+    "connector": {},
 }
 
 

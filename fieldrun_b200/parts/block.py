@@ -1,12 +1,13 @@
 """The arrangement of a layer: norm -> mixer -> residual, norm -> feed-forward -> residual
 (the reference's two-norm pre-norm block, src/minimax.rs:261-284).  Each residual sum is
 left to the norm that follows it, which adds in float32 while it reads the stream.
-A second arrangement, ``output_norm``, has the norm behind the sublayer instead of in front of it."""
+A second arrangement, ``output_norm``, has the norm behind the sublayer instead of in front of it; a third,
+``parallel_pre_norm``, runs the two sublayers side by side on the same x."""
 from __future__ import annotations
 
 import torch
 
-from .base import Block, as_tensor, register_part
+from .base import Block, UpdateSum, as_tensor, register_part
 from .norm import LayerNorm
 
 
@@ -53,5 +54,29 @@ class OutputNormBlock(Block):
         return x, None
 
 
+class ParallelPreNormBlock(Block):
+    """Both sublayers side by side: x <- x + mixer(norm1(x)) + feed_forward(norm2(x)), the two norms reading the same
+    x.  Their outputs are left unsummed (``UpdateSum``) for the norm that reads the stream next.  Two norms of a kind
+    that has ``forward_pair`` run as one kernel."""
+
+    def forward(self, ctx, x, pending, line, writes_cache):
+        ff, norm1, norm2 = self.feed_forward, self.mixer_norm, self.feed_forward_norm
+        want32 = ff is not None and ff.wants_float32_input
+        if ff is not None and hasattr(norm1, "forward_pair") and type(norm1) is type(norm2):
+            act1, act2, act2_32 = norm1.forward_pair(ctx, x, norm2, delta=pending, want32=want32)
+            update = self.mixer.forward(ctx, act1, line, writes_cache)
+        else:
+            if not norm1.accepts_deferred:
+                pending = as_tensor(ctx, pending)
+            act1, _ = norm1.forward(ctx, x, delta=pending)
+            update = self.mixer.forward(ctx, act1, line, writes_cache)       # before the second norm takes the buffer
+            if ff is not None:
+                act2, act2_32 = norm2.forward(ctx, x, want32=want32)
+        if ff is None:
+            return x, update
+        return x, UpdateSum([as_tensor(ctx, update), ff.forward_deferred(ctx, act2, act2_32)])
+
+
+register_part("block", "parallel_pre_norm", ParallelPreNormBlock, replace=True)
 register_part("block", "pre_norm", PreNormBlock, replace=True)
 register_part("block", "output_norm", OutputNormBlock, replace=True)

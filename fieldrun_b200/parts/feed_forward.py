@@ -1,7 +1,8 @@
 """Feed-forward parts: experts chosen by a router, and a dense gated unit.
 
 Routed experts (src/minimax.rs:88-126): router logits z = act W_r^T in float32;
-score s = sigmoid(z); choice c = s + bias (the bias decides only who is picked);
+score s = sigmoid(z) (or, with ``score: softmax``, the softmax of z over all experts; ``weight_floor`` then adds
+1e-20 to the sum of the picked scores); choice c = s + bias (the bias decides only who is picked);
 the ``top_k`` largest c, ties to the lower id; weights s / sum of the picked s;
 each picked expert computes silu(x W1^T) * (x W3^T) then W2; the outputs are
 summed with their weights in rank order.  The experts' matrices are stacked:
@@ -43,10 +44,17 @@ class RoutedExperts(FeedForward):
         self.num_experts = int(a["num_experts"])
         self.top_k = int(a["top_k"])
         self.expert_width = int(a["expert_width"])
-        if a.get("score", "sigmoid") != "sigmoid":
-            raise ValueError(f"router score {a.get('score')!r}: only 'sigmoid' is built")
+        self.score = a.get("score", "sigmoid")
+        if self.score not in ("sigmoid", "softmax"):
+            raise ValueError(f"router score {self.score!r} is neither 'sigmoid' nor 'softmax'")
         self.choice_bias = bool(a.get("choice_bias", False))
-        self.renormalize = bool(a.get("renormalize", True))
+        floor = float(a.get("weight_floor") or 0.0)
+        if floor not in (0.0, ops.ROUTE_WEIGHT_FLOOR):
+            raise ValueError(f"a floor of {floor} under the sum of the picked scores: the kernels have 0 and {ops.ROUTE_WEIGHT_FLOOR}")
+        # what the kernels take as their ``renormalize``: bit 0 divides by the sum of the picked scores, bit 1 makes the
+        # scores a softmax over all experts (else sigmoids), bit 2 adds the floor to that sum
+        self.renormalize = (int(bool(a.get("renormalize", True))) | (ops.ROUTE_SOFTMAX if self.score == "softmax" else 0)
+                            | (ops.ROUTE_FLOOR if floor else 0))
         self.routed_scale = float(a.get("routed_scale", 1.0))
         if not 1 <= self.top_k <= self.num_experts:
             raise ValueError(f"top_k {self.top_k} is outside 1..{self.num_experts} experts")

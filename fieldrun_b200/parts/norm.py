@@ -9,7 +9,7 @@ import torch
 
 from ..csrc import ops
 from ..weights.loader import VECTOR, TensorNeed, TensorSource
-from .base import Norm, WeightedRows, as_tensor, register_part
+from .base import Norm, UpdateSum, WeightedRows, as_tensor, register_part
 
 
 class RMSNorm(Norm):
@@ -101,5 +101,77 @@ class LayerNorm(Norm):
         return act
 
 
+class DynamicTanh(Norm):
+    """tanh(alpha v) * weight + bias with one learned scalar alpha: a norm without statistics.  Two of them that read
+    the same stream (a block whose sublayers run side by side) go through one kernel (``forward_pair``), which also
+    adds the updates that the block before left: float32 tensors and the experts' weighted rows."""
+
+    replayable = True
+    accepts_deferred = True
+
+    def __init__(self, spec, dtype):
+        super().__init__(spec, dtype)
+        self.width = int(spec.args["width"])
+        self.weight: Optional[torch.Tensor] = None
+        self.bias: Optional[torch.Tensor] = None
+        self.alpha: Optional[torch.Tensor] = None
+
+    def tensor_needs(self):
+        return [TensorNeed(self.name_of("weight"), (self.width,), VECTOR, "around_one"),
+                TensorNeed(self.name_of("bias"), (self.width,), VECTOR, "bias"),
+                TensorNeed(self.name_of("alpha"), (), VECTOR, "around_half")]
+
+    def load(self, source: TensorSource) -> None:
+        self.weight, self.bias, alpha = (source.fetch(need) for need in self.tensor_needs())
+        self.alpha = alpha.reshape(1)                    # stays on the device: the kernel reads it there
+
+    def triple(self):
+        return self.weight, self.bias, self.alpha
+
+    @staticmethod
+    def split(ctx, delta):
+        """(float32 tensors, experts' rows or None) of whatever form the update came in."""
+        if delta is None:
+            return (), None
+        if isinstance(delta, torch.Tensor):
+            return (delta,), None
+        if isinstance(delta, WeightedRows) and delta.top_k <= ops.NORM_MAX_SUMMED_ROWS:
+            return (), (delta.rows, delta.weights, delta.row_map)
+        if isinstance(delta, UpdateSum) and len(delta.tensors) <= 2 and all(
+                w.top_k <= ops.NORM_MAX_SUMMED_ROWS for w in delta.weighted):
+            weighted = delta.weighted[0] if delta.weighted else None
+            return tuple(delta.tensors), (weighted.rows, weighted.weights, weighted.row_map) if weighted else None
+        return (as_tensor(ctx, delta),), None
+
+    def forward(self, ctx, x, *, delta=None, rows=None, want32=False, write_back=True):
+        deltas, experts = self.split(ctx, delta)
+        count = rows.numel() if rows is not None else x.shape[0]
+        out = ctx.buffer(f"norm.out.{self.width}", (count, self.width), self.dtype)
+        ops.dyt_norm(x, self.triple(), out, deltas=deltas, experts=experts, rows=rows,
+                     write_back=write_back and rows is None and (bool(deltas) or experts is not None))
+        out32 = None
+        if want32:
+            out32 = out
+            if self.dtype != torch.float32:
+                out32 = ctx.buffer(f"norm.out32.{self.width}", (count, self.width), torch.float32)
+                ops.dyt_norm(x, self.triple(), out32, rows=rows)       # x holds the sum by now (or nothing was added)
+        return out, out32
+
+    def forward_pair(self, ctx, x, other: "DynamicTanh", *, delta=None, want32=False):
+        """This norm and ``other`` of the same x + delta (the sum stored back): (out, other's out, other's out in
+        float32 or None)."""
+        deltas, experts = self.split(ctx, delta)
+        rows = x.shape[0]
+        out1 = ctx.buffer(f"norm.out.{self.width}", (rows, self.width), self.dtype)
+        out2 = ctx.buffer(f"norm.out2.{self.width}", (rows, self.width), self.dtype)
+        out2_32 = None
+        if want32 and self.dtype != torch.float32:
+            out2_32 = ctx.buffer(f"norm.out32.{self.width}", (rows, self.width), torch.float32)
+        ops.dyt_norm(x, self.triple(), out1, second=other.triple(), out2=out2, out2_32=out2_32, deltas=deltas, experts=experts,
+                     write_back=bool(deltas) or experts is not None)
+        return out1, out2, (out2 if self.dtype == torch.float32 else out2_32) if want32 else None
+
+
+register_part("norm", "dynamic_tanh", DynamicTanh, replace=True)
 register_part("norm", "rmsnorm", RMSNorm, replace=True)
 register_part("norm", "layernorm", LayerNorm, replace=True)
