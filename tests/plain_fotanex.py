@@ -55,19 +55,29 @@ def chunked_sink_attention(h, q_w, k_w, v_w, sink, gate_w, o_w, *, heads, kv_hea
     q = (h @ q_w.T).reshape(count, heads, dim)
     k = (h @ k_w.T).reshape(count, kv_heads, dim)
     v = (h @ v_w.T).reshape(count, kv_heads, vdim)
-    gate = sigmoid(h @ gate_w.T)                                   # [T, heads]
-    out = np.zeros((count, heads, vdim))
-    per = heads // kv_heads
-    for head in range(heads):
-        g = head // per
-        for i in range(count):
-            first = (i // chunk) * chunk
-            scores = (k[first:i + 1, g] @ q[i, head]) * scale
-            top = max(scores.max(), sink[head])
-            weights = np.exp(scores - top)
-            denom = weights.sum() + np.exp(sink[head] - top)
-            out[i, head] = (weights / denom) @ v[first:i + 1, g] * gate[i, head]
+    out = attend_in_chunks(q, k, v, sink, h @ gate_w.T, scale, chunk)
     return out.reshape(count, heads * vdim) @ o_w.T
+
+
+def attend_in_chunks(q, k, v, sink, gate_logits, scale, chunk, positions=None):
+    """q [R, heads, dim] at ``positions`` (default: row r is position r) over k [T, G, dim], v [T, G, vdim];
+    ``sink`` [heads] or None; ``gate_logits`` [R, heads] or None; ``chunk`` None: every earlier key."""
+    rows, heads = q.shape[0], q.shape[1]
+    per = heads // k.shape[1]
+    out = np.zeros((rows, heads, v.shape[2]))
+    for r in range(rows):
+        i = r if positions is None else int(positions[r])
+        first = (i // chunk) * chunk if chunk else 0
+        for head in range(heads):
+            g = head // per
+            scores = (k[first:i + 1, g] @ q[r, head]) * scale
+            top = scores.max() if sink is None else max(scores.max(), sink[head])
+            weights = np.exp(scores - top)
+            denom = weights.sum() + (np.exp(sink[head] - top) if sink is not None else 0.0)
+            out[r, head] = (weights / denom) @ v[first:i + 1, g]
+            if gate_logits is not None:
+                out[r, head] *= sigmoid(gate_logits[r, head])
+    return out
 
 
 def selective_scan(h, in_w, conv_w, conv_b, x_w, dt_w, dt_b, a_log, d, o_w, *, inner, state, dt_rank):
@@ -78,13 +88,18 @@ def selective_scan(h, in_w, conv_w, conv_b, x_w, dt_w, dt_b, a_log, d, o_w, *, i
     low = x @ x_w.T
     dt = softplus(low[:, :dt_rank] @ dt_w.T + dt_b)                # [T, inner]
     b, c = low[:, dt_rank:dt_rank + state], low[:, dt_rank + state:]
-    a = -np.exp(a_log)                                             # [inner, state]
-    s = np.zeros((inner, state))
+    return (selective_recurrence(x, dt, b, c, a_log, d) * silu(z)) @ o_w.T
+
+
+def selective_recurrence(x, dt, b, c, a_log, d):
+    """x, dt [T, inner]; b, c [T, state]; a_log [inner, state]; d [inner] -> y [T, inner], from a zero state."""
+    a = -np.exp(a_log)
+    s = np.zeros(a_log.shape)
     y = np.zeros_like(x)
-    for t in range(h.shape[0]):
+    for t in range(x.shape[0]):
         s = np.exp(dt[t][:, None] * a) * s + (dt[t] * x[t])[:, None] * b[t][None, :]
         y[t] = s @ c[t] + d * x[t]
-    return (y * silu(z)) @ o_w.T
+    return y
 
 
 def parallel_mixer(h, left, right, left_norm, right_norm, eps):
@@ -105,14 +120,18 @@ def rglru(h, y_w, y_b, x_w, x_b, conv_w, conv_b, ra, ra_b, ri, ri_b, lam, o_w, *
         cols = slice(b * part, (b + 1) * part)
         r[:, cols] = sigmoid(u[:, cols] @ ra[b].T + ra_b[b])
         i[:, cols] = sigmoid(u[:, cols] @ ri[b].T + ri_b[b])
-    log_a = -8.0 * r * softplus(lam)
-    a = np.exp(log_a)
-    s = np.zeros(width)
+    return (gated_recurrence(u, r, i, lam) * y) @ o_w.T
+
+
+def gated_recurrence(u, r, i, lam, constant=8.0):
+    """u, r, i [T, width] (the gates after their sigmoids), lam [width] -> the states [T, width], from zero."""
+    a = np.exp(-constant * r * softplus(lam))
+    s = np.zeros(u.shape[1])
     out = np.zeros_like(u)
-    for t in range(count):
+    for t in range(u.shape[0]):
         s = a[t] * s + np.sqrt(1.0 - a[t] ** 2) * i[t] * u[t]
         out[t] = s
-    return (out * y) @ o_w.T
+    return out
 
 
 def mamba2(h, in_w, conv_w, conv_b, dt_bias, a_log, d, norm_w, o_w, *, heads, vdim, state, groups, norm_groups, eps):
@@ -125,35 +144,48 @@ def mamba2(h, in_w, conv_w, conv_b, dt_bias, a_log, d, norm_w, o_w, *, heads, vd
     x = xbc[:, :inner].reshape(-1, heads, vdim)
     b = xbc[:, inner:inner + groups * state].reshape(-1, groups, state)
     c = xbc[:, inner + groups * state:].reshape(-1, groups, state)
-    per = heads // groups
-    s = np.zeros((heads, state, vdim))
-    y = np.zeros((h.shape[0], heads, vdim))
-    for t in range(h.shape[0]):
+    y = state_space_recurrence(x, b, c, dt, a_log, d).reshape(-1, inner) * silu(z)
+    return group_rms(y, norm_w, norm_groups, eps) @ o_w.T
+
+
+def state_space_recurrence(x, b, c, dt, a_log, d):
+    """x [T, heads, vdim]; b, c [T, groups, state]; dt [T, heads]; a_log, d [heads] -> y [T, heads, vdim], from zero."""
+    heads, vdim = x.shape[1], x.shape[2]
+    per = heads // b.shape[1]
+    s = np.zeros((heads, b.shape[2], vdim))
+    y = np.zeros_like(x)
+    for t in range(x.shape[0]):
         for head in range(heads):
             g = head // per
             s[head] = np.exp(-np.exp(a_log[head]) * dt[t, head]) * s[head] + dt[t, head] * np.outer(b[t, g], x[t, head])
             y[t, head] = s[head].T @ c[t, g] + d[head] * x[t, head]
-    y = y.reshape(-1, inner) * silu(z)
-    y = rms_divide(y.reshape(-1, norm_groups, inner // norm_groups), eps).reshape(-1, inner) * norm_w
-    return y @ o_w.T
+    return y
 
 
-def routed_experts(h, router_w, experts, top):
+def group_rms(y, weight, parts, eps):
+    """Rows in ``parts`` equal parts, each divided by its own root mean square, times the weight."""
+    return rms_divide(y.reshape(y.shape[0], parts, -1), eps).reshape(y.shape) * weight
+
+
+def routed_experts(h, router_w, experts, top, forced=None):
     """``experts``: list of (gate, up, down).  Softmax over all experts, the ``top`` largest, their scores divided by
-    their sum (+ 1e-20)."""
+    their sum (+ 1e-20).  ``forced`` [T, top] names the experts to use instead of the largest.  Returns the output,
+    the experts used and, per token, the gap between the last score taken and the first one left out."""
     logits = h @ router_w.T
     scores = np.exp(logits - logits.max(axis=-1, keepdims=True))
     scores /= scores.sum(axis=-1, keepdims=True)
     out = np.zeros_like(h)
     picked = np.zeros((h.shape[0], top), dtype=np.int64)
+    ranked = -np.sort(-scores, axis=-1)
+    margins = ranked[:, top - 1] - ranked[:, top] if top < scores.shape[1] else np.full(h.shape[0], np.inf)
     for t in range(h.shape[0]):
-        order = np.argsort(-scores[t], kind="stable")[:top]
+        order = np.argsort(-scores[t], kind="stable")[:top] if forced is None else np.asarray(forced[t], dtype=np.int64)
         picked[t] = order
         weights = scores[t, order] / (scores[t, order].sum() + 1e-20)
         for e, w in zip(order, weights):
             gate, up, down = experts[e]
             out[t] += w * (down @ (silu(gate @ h[t]) * (up @ h[t])))
-    return out, picked
+    return out, picked, margins
 
 
 # ---------------------------------------------------------------------------------------------------- the model
@@ -190,16 +222,18 @@ def mixer_of(config, tensors, index, h):
     raise ValueError(f"layer type {kind!r}")
 
 
-def feed_forward_of(config, tensors, index, h, picks=None):
+def feed_forward_of(config, tensors, index, h, picks=None, forced=None):
+    """``picks`` (a list) receives (experts used, margins) of this run; ``forced`` (a list) gives up its first entry."""
     mlp = config["layers"][index]["mlp"]
     if mlp is None:
         return np.zeros_like(h)
     p = f"l{index}.mlp."
     count = mlp["router"]["experts"]
     experts = [(tensors[f"{p}e{e}.gate"], tensors[f"{p}e{e}.up"], tensors[f"{p}e{e}.down"]) for e in range(count)]
-    out, picked = routed_experts(h, tensors[p + "router"], experts, mlp["router"]["top"])
+    out, picked, margins = routed_experts(h, tensors[p + "router"], experts, mlp["router"]["top"],
+                                          forced.pop(0) if forced is not None else None)
     if picks is not None:
-        picks.append(picked)
+        picks.append((picked, margins))
     return out
 
 
@@ -217,15 +251,19 @@ def run_order(config):
     return order
 
 
-def forward(config, tensors, tokens, layers_out=None, picks=None):
-    """Logits [T, vocab] of one sequence.  ``layers_out`` (a list) receives the stream after every layer run."""
+def forward(config, tensors, tokens, layers_out=None, picks=None, forced=None):
+    """Logits [T, vocab] of one sequence.  ``layers_out`` (a list) receives the stream after every layer run,
+    ``picks`` the experts of every run that has some; ``forced`` lists, in that order, the experts to use instead."""
+    forced = list(forced) if forced is not None else None
     x0 = tensors["embed"][np.asarray(tokens)]
     x = x0.copy()
     for index, opens in run_order(config):
         if opens is not None:
             x = np.concatenate([x, x0], axis=1) @ tensors["loop.in"].T + tensors["loop.step"][opens]
-        x = x + (mixer_of(config, tensors, index, _norm(tensors, f"l{index}.norm1", x))
-                 + feed_forward_of(config, tensors, index, _norm(tensors, f"l{index}.norm2", x), picks))
+        update = mixer_of(config, tensors, index, _norm(tensors, f"l{index}.norm1", x))
+        if config["layers"][index]["mlp"] is not None:
+            update = update + feed_forward_of(config, tensors, index, _norm(tensors, f"l{index}.norm2", x), picks, forced)
+        x = x + update
         if layers_out is not None:
             layers_out.append(x.copy())
     return _norm(tensors, "final.norm", x) @ tensors["head"].T
