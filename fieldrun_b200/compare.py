@@ -3,7 +3,10 @@
 ``python bench.py --design bamasun`` prints what :func:`compare_designs` returns.  For each size it builds a Bamasun
 model (attention, recurrent and key-sharing layers in turn, dense feed-forward) and a MiniMax-M2 model of the same
 width, heads, head size, layers and vocabulary whose feed-forward is a single expert of two thirds the width (three
-matrices instead of two: the same weights and multiply-adds), both with random weights in bfloat16, and measures
+matrices instead of two: the same weights and multiply-adds), both with random weights in bfloat16.
+``--design fotanex`` does the same for a Fotanex model (a gated linear recurrence, a state-space layer and two layers
+of chunked attention beside a selective scan in turn, every layer with routed experts) beside a MiniMax-M2 model with
+the same experts.  It measures
 
 * a step of prompts (tokens a second, CUDA events around the step, after warm-up steps);
 * decode steps at two batch sizes from those prompts (tokens a second; the tokens stay on the device);
@@ -49,7 +52,39 @@ def bamasun_config(width, heads, kv_heads, dim, ff, layers, vocab) -> dict[str, 
             "logit_softcap": 30.0, "layers": listed}
 
 
-def minimax_config(width, heads, kv_heads, dim, ff, layers, vocab) -> dict[str, Any]:
+# the routed experts of the Fotanex comparison, on both sides: how many, how many a token uses, and their width as a
+# share of the size's feed-forward width
+FOTANEX_EXPERTS, FOTANEX_TOP, FOTANEX_FF_SHARE = 16, 2, 4
+FOTANEX_CHUNK = 1024         # positions of an attention chunk: a prompt of 2,048 tokens has two
+
+
+def fotanex_config(width, heads, kv_heads, dim, ff, layers, vocab) -> dict[str, Any]:
+    """Layers in turns of four: gated linear recurrence, state-space layer, then twice chunked attention beside a
+    selective scan; sizes as published models of these kinds have them at this width."""
+    mlp = {"kind": "moe", "expert": {"ff": ff // FOTANEX_FF_SHARE // 128 * 128}, "router": {"experts": FOTANEX_EXPERTS, "top": FOTANEX_TOP}}
+    listed = []
+    for index in range(layers):
+        turn = index % 4
+        if turn == 0:
+            listed.append({"type": "rglru", "mixer": {"width": width, "blocks": heads, "conv": 4}, "mlp": mlp})
+        elif turn == 1:
+            listed.append({"type": "mamba2", "mixer": {"heads": 2 * width // 64, "vdim": 64, "state": 128, "groups": 8,
+                                                       "norm_groups": 1, "conv": 4}, "mlp": mlp})
+        else:
+            listed.append({"type": "parallel", "mixer": {
+                "left": {"heads": heads, "kv_heads": kv_heads, "dim": dim, "vdim": dim, "scale": dim ** -0.5,
+                         "mask": {"size": FOTANEX_CHUNK}},
+                "right": {"inner": 2 * width, "state": 16, "dt_rank": width // 16, "conv": 4}}, "mlp": mlp})
+    return {"architecture": "Fotanex", "vocab": vocab, "width": width, "norm": {"eps": 1e-6}, "layers": listed}
+
+
+def minimax_config(width, heads, kv_heads, dim, ff, layers, vocab, experts=None) -> dict[str, Any]:
+    if experts is not None:
+        count, top, expert_ff = experts
+        return dict(architectures=["MiniMaxM2ForCausalLM"], model_type="minimax_m2", hidden_size=width, num_attention_heads=heads,
+                    num_key_value_heads=kv_heads, head_dim=dim, rotary_dim=dim // 2, rope_theta=1000000.0, use_qk_norm=True,
+                    num_local_experts=count, num_experts_per_tok=top, intermediate_size=expert_ff,
+                    vocab_size=vocab, rms_norm_eps=1e-6, tie_word_embeddings=False, num_hidden_layers=layers)
     return dict(architectures=["MiniMaxM2ForCausalLM"], model_type="minimax_m2", hidden_size=width, num_attention_heads=heads,
                 num_key_value_heads=kv_heads, head_dim=dim, rotary_dim=dim // 2, rope_theta=1000000.0, use_qk_norm=True,
                 num_local_experts=1, num_experts_per_tok=1, intermediate_size=(2 * ff // 3 + 127) // 128 * 128,
@@ -126,19 +161,24 @@ def _measure(lm, vocab: int, steps: int, warmup: int, decode_batches=(8, 64)) ->
     return out
 
 
-def compare_designs(sizes=("w2048", "w4096"), steps: int = 8, warmup: int = 3) -> dict[str, Any]:
+def compare_designs(sizes=("w2048", "w4096"), steps: int = 8, warmup: int = 3, design: str = "bamasun") -> dict[str, Any]:
     import fieldrun_b200 as fr
     result: dict[str, Any] = {"prompt_tokens": PROMPT, "prompts_per_step": PROMPTS_PER_STEP, "dtype": "bf16",
                               "data": "synthetic tokens, random weights", "sizes": {}}
     for name in sizes:
         size = SIZES[name]
         entry: dict[str, Any] = {"size": size}
-        for design, config in (("bamasun", bamasun_config(**size)), ("minimax_m2", minimax_config(**size))):
+        if design == "fotanex":
+            experts = (FOTANEX_EXPERTS, FOTANEX_TOP, size["ff"] // FOTANEX_FF_SHARE // 128 * 128)
+            pair = (("fotanex", fotanex_config(**size)), ("minimax_m2", minimax_config(**size, experts=experts)))
+        else:
+            pair = (("bamasun", bamasun_config(**size)), ("minimax_m2", minimax_config(**size)))
+        for design_name, config in pair:
             began = time.time()
             lm = fr.random_model(config, fr.RandomInit(seed=1, matrix_std=0.02, norm_std=0.1, bias_std=0.02), dtype="bfloat16",
                                  max_tokens=64 * (PROMPT + 256), num_slots=72, max_batch=64)
-            entry[design] = _measure(lm, size["vocab"], steps, max(warmup, 3))
-            entry[design]["build_s"] = round(time.time() - began, 1)
+            entry[design_name] = _measure(lm, size["vocab"], steps, max(warmup, 3))
+            entry[design_name]["build_s"] = round(time.time() - began, 1)
             del lm
             torch.cuda.empty_cache()
         result["sizes"][name] = entry

@@ -67,7 +67,7 @@ attention_decode_tma_kernel(const __grid_constant__ CUtensorMap map_k, const __g
     const int group = p.num_heads / p.num_kv_heads;
     const int pos = p.seq_pos[b];
     const int slot = p.seq_slot[b];               // asked for together with the position: one wait, not two
-    const int hi_key = pos, lo_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int hi_key = pos, lo_key = first_visible_key(pos, p.window, p.chunk);
     // the pages of this block that hold a key the token may see
     const int pages_per_block = params.chunks_per_block * DT_CHUNK_PAGES;
     const int first_page = max(part * pages_per_block, lo_key / FRB_PAGE);
@@ -304,13 +304,14 @@ __global__ void __launch_bounds__(HD) attention_decode_tma_merge_kernel(DecodeTm
     const DecodeAttnParams& p = params.a;
     const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const int pos = p.seq_pos[b];
-    const int lo_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int lo_key = first_visible_key(pos, p.window, p.chunk);
     const int keys_per_block = params.chunks_per_block * ATT_CHUNK;
     // never beyond the partial results the launch has room for, whatever the position says
     const int last = min(pos / keys_per_block, p.max_chunks - 1), first = min(lo_key / keys_per_block, last);
     if (pos / keys_per_block >= p.max_chunks && d == 0) atomicExch(params.status, FRB_STATUS_TOO_LONG);   // keys were left out
     const size_t row0 = ((size_t)b * p.num_heads + head) * p.max_chunks;
-    p.out[((size_t)b * p.num_heads + head) * HD + d] = __float2bfloat16_rn(merged_element<HD>(p.part_ml, p.part_o, row0, first, last, d));
+    p.out[((size_t)b * p.num_heads + head) * HD + d] = __float2bfloat16_rn(merged_element<HD>(p.part_ml, p.part_o, row0, first, last, d,
+                                                                                                    p.sinks ? p.sinks[head] * 1.4426950408889634f : -INFINITY));
 }
 
 // As frb_attention_decode_mma, for head sizes 64 and 128.  num_pages: pages of the cache group (the tensor
@@ -322,7 +323,7 @@ FRB_API int frb_attention_decode_tma(const void* q, const void* k_pages, const v
                                      const int* page_table, int max_pages, const int* seq_pos, const int* seq_slot,
                                      float* part_o, float* part_ml, void* out, int num_seqs, int num_heads, int num_kv_heads,
                                      int head_dim, float scale, int window, int max_chunks, int chunks_per_block, int* status,
-                                     const float* slopes, cudaStream_t stream) {
+                                     const float* slopes, int chunk, const float* sinks, cudaStream_t stream) {
     if (num_seqs == 0) return 0;
     const int group = num_kv_heads > 0 ? num_heads / num_kv_heads : 0;
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0 && group <= 16,
@@ -342,6 +343,7 @@ FRB_API int frb_attention_decode_tma(const void* q, const void* k_pages, const v
     p.seq_pos = seq_pos; p.seq_slot = seq_slot; p.part_o = part_o; p.part_ml = part_ml; p.out = (bf16*)out;
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
     p.num_kv_heads = num_kv_heads; p.max_chunks = parts; p.status = status; p.slopes = slopes;
+    p.chunk = chunk; p.sinks = sinks;
     params.chunks_per_block = chunks_per_block; params.status = status;
     static const int early = [] { const char* v = getenv("FIELDRUN_B200_ATTENTION_EARLY"); return !(v && v[0] == '0'); }();
     params.early = early;

@@ -5,10 +5,11 @@
 FRB_API int frb_attention_decode_mma(const void* q, const void* k_pages, const void* v_pages, const int* page_table,
                                      int max_pages, const int* seq_pos, const int* seq_slot, float* part_o, float* part_ml,
                                      void* out, int num_seqs, int num_heads, int num_kv_heads, int head_dim, float scale,
-                                     int window, int max_chunks, int* status, const float* slopes, cudaStream_t stream) {
+                                     int window, int max_chunks, int* status, const float* slopes, int chunk, const float* sinks,
+                                     cudaStream_t stream) {
     return launch_attention_decode("attention_decode_mma", q, k_pages, v_pages, page_table, max_pages, seq_pos, seq_slot,
                                    part_o, part_ml, out, num_seqs, num_heads, num_kv_heads, head_dim, scale, window,
-                                   max_chunks, stream, status, slopes);
+                                   max_chunks, stream, status, slopes, chunk, sinks);
 }
 
 // ----------------------------------------------------------------------------- many tokens per sequence
@@ -28,6 +29,8 @@ struct PrefillAttnParams {
     float scale2;
     int window, max_pages, num_heads, num_kv_heads;
     const float* slopes;       // null, or one slope per query head: key j's score is lowered by slope * (position - j)
+    int chunk;                 // 0, or a query sees only the keys of its own chunk of this many positions
+    const float* sinks;        // null, or one number per query head whose exponential joins the softmax's denominator
 };
 
 __device__ __forceinline__ void cp_async16(void* dst, const void* src) {
@@ -68,10 +71,10 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS <= 6 ? 2 : 1) attent
         const int row = g + 8 * r;
         valid[r] = q0 + row < q_len;
         hi[r] = valid[r] ? start + q0 + row : -1;
-        lo[r] = (valid[r] && p.window > 0) ? max(0, hi[r] - p.window + 1) : 0;
+        lo[r] = valid[r] ? first_visible_key(hi[r], p.window, p.chunk) : 0;
     }
     const int last_key = start + min(q0 + 15, q_len - 1);
-    const int first_key = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
+    const int first_key = first_visible_key(start + q0, p.window, p.chunk);
     const int first_page = first_key / FRB_PAGE, last_page = last_key / FRB_PAGE;
     for (int hbase = 0; hbase < group; hbase += nwarps) {
         const int hl = hbase + warp;
@@ -107,7 +110,13 @@ __global__ void __launch_bounds__(MAX_WARPS * 32, MAX_WARPS <= 6 ? 2 : 1) attent
 #pragma unroll
             for (int r = 0; r < 2; ++r) {
                 if (!valid[r]) continue;
-                const float inv = 1.0f / st.l[r];
+                float scale_o = 1.f, total = st.l[r];
+                if (p.sinks) {                              // the sink joins the denominator (log2 units, like st.m)
+                    const float sink2 = p.sinks[head] * 1.4426950408889634f, top = fmaxf(st.m[r], sink2);
+                    scale_o = exp2f(st.m[r] - top);
+                    total = total * scale_o + exp2f(sink2 - top);
+                }
+                const float inv = scale_o / total;
                 bf16* dst = p.out + ((size_t)(tok0 + g + 8 * r) * p.num_heads + head) * HD;
 #pragma unroll
                 for (int n = 0; n < HD / 8; ++n)
@@ -121,7 +130,7 @@ FRB_API int frb_attention_prefill_mma(const void* q, const void* k_pages, const 
                                       int max_pages, const int* tile_seq, const int* tile_q0, int num_tiles,
                                       const int* seq_slot, const int* seq_start, const int* seq_q_len, const int* cu_q_len,
                                       void* out, int num_heads, int num_kv_heads, int head_dim, float scale, int window,
-                                      const float* slopes, cudaStream_t stream) {
+                                      const float* slopes, int chunk, const float* sinks, cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0, "attention: %d heads over %d kv heads", num_heads, num_kv_heads);
     FRB_CHECK_ARG(head_dim == 32 || head_dim == 64 || head_dim == 96 || head_dim == 128,
@@ -132,6 +141,7 @@ FRB_API int frb_attention_prefill_mma(const void* q, const void* k_pages, const 
     p.tile_seq = tile_seq; p.tile_q0 = tile_q0; p.seq_slot = seq_slot; p.seq_start = seq_start; p.seq_q_len = seq_q_len;
     p.cu_q_len = cu_q_len; p.out = (bf16*)out; p.scale2 = scale * 1.4426950408889634f; p.window = window;
     p.max_pages = max_pages; p.num_heads = num_heads; p.num_kv_heads = num_kv_heads; p.slopes = slopes;
+    p.chunk = chunk; p.sinks = sinks;
     const int group = num_heads / num_kv_heads;
     const int nwarps = group < 8 ? group : 8;
     dim3 grid(num_tiles, num_kv_heads);

@@ -188,6 +188,8 @@ struct DecodeAttnParams {
     int window, max_pages, num_heads, num_kv_heads, max_chunks;
     int* status;               // null, or a word that gets FRB_STATUS_TOO_LONG when a sequence has more chunks than max_chunks
     const float* slopes;       // null, or one slope per query head: key j's score is lowered by slope * (position - j)
+    int chunk;                 // 0, or the token sees only the keys of its own chunk of this many positions
+    const float* sinks;        // null, or one number per query head whose exponential joins the softmax's denominator
 };
 
 // The slopes of the two query heads that a thread's rows g and g + 8 of the group's tile stand for, times log2(e).
@@ -211,7 +213,7 @@ __global__ void __launch_bounds__(128, 4) attention_decode_mma_kernel(DecodeAttn
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, g = lane >> 2, t = lane & 3;
     const int group = p.num_heads / p.num_kv_heads;
     const int pos = p.seq_pos[b];
-    const int hi_key = pos, lo_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int hi_key = pos, lo_key = first_visible_key(pos, p.window, p.chunk);
     if (chunk * ATT_CHUNK > hi_key || (chunk + 1) * ATT_CHUNK <= lo_key) return;      // the merge skips these chunks
 
     const int page_index = chunk * (ATT_CHUNK / FRB_PAGE) + warp;
@@ -336,7 +338,7 @@ __global__ void __launch_bounds__(128, 4) attention_decode_mma_kernel(DecodeAttn
 // the merge's time.
 template <int HD>
 __device__ __forceinline__ float merged_element(const float* __restrict__ part_ml, const float* __restrict__ part_o, size_t row0,
-                                                int first, int last, int d) {
+                                                int first, int last, int d, float sink2 = -INFINITY) {
     constexpr int AT_ONCE = 8;
     float top = -INFINITY, sum = 0.f, acc = 0.f;
     for (int c0 = first; c0 <= last; c0 += AT_ONCE) {
@@ -365,6 +367,12 @@ __device__ __forceinline__ float merged_element(const float* __restrict__ part_m
                 acc += o[u] * f;
             }
     }
+    if (sink2 > -INFINITY) {                              // a sink: a term of the denominator without a value (log2 units)
+        const float top_all = fmaxf(top, sink2);
+        const float keep = exp2f(top - top_all);
+        sum = sum * keep + exp2f(sink2 - top_all);
+        acc *= keep;
+    }
     return acc / sum;
 }
 
@@ -374,13 +382,14 @@ __global__ void __launch_bounds__(HD) attention_decode_merge_kernel(DecodeAttnPa
     after_previous_kernel();
     const int head = blockIdx.x, b = blockIdx.y, d = threadIdx.x;
     const int pos = p.seq_pos[b];
-    const int lo_key = p.window > 0 ? max(0, pos - p.window + 1) : 0;
+    const int lo_key = first_visible_key(pos, p.window, p.chunk);
     // never beyond the partial results the launch has room for, whatever the position says (the caller's
     // max_chunks covers the longest sequence; a smaller one must not make this read another row's results)
     const int last = min(pos / ATT_CHUNK, p.max_chunks - 1), first = min(lo_key / ATT_CHUNK, last);
     if (pos / ATT_CHUNK >= p.max_chunks && p.status && d == 0) atomicExch(p.status, FRB_STATUS_TOO_LONG);   // keys were left out
     const size_t row0 = ((size_t)b * p.num_heads + head) * p.max_chunks;
-    p.out[((size_t)b * p.num_heads + head) * HD + d] = __float2bfloat16_rn(merged_element<HD>(p.part_ml, p.part_o, row0, first, last, d));
+    p.out[((size_t)b * p.num_heads + head) * HD + d] = __float2bfloat16_rn(merged_element<HD>(p.part_ml, p.part_o, row0, first, last, d,
+                                                                                                    p.sinks ? p.sinks[head] * 1.4426950408889634f : -INFINITY));
 }
 
 // Checks the sizes and launches the one-token kernel and its merge.  `what` names the caller in errors.
@@ -388,7 +397,8 @@ static inline int launch_attention_decode(const char* what, const void* q, const
                                           const int* page_table, int max_pages, const int* seq_pos, const int* seq_slot,
                                           float* part_o, float* part_ml, void* out, int num_seqs, int num_heads,
                                           int num_kv_heads, int head_dim, float scale, int window, int max_chunks,
-                                          cudaStream_t stream, int* status = nullptr, const float* slopes = nullptr) {
+                                          cudaStream_t stream, int* status = nullptr, const float* slopes = nullptr,
+                                          int chunk = 0, const float* sinks = nullptr) {
     if (num_seqs == 0) return 0;
     const int group = num_kv_heads > 0 ? num_heads / num_kv_heads : 0;
     FRB_CHECK_ARG(num_kv_heads > 0 && num_heads % num_kv_heads == 0 && group <= 16,
@@ -401,6 +411,7 @@ static inline int launch_attention_decode(const char* what, const void* q, const
     p.seq_pos = seq_pos; p.seq_slot = seq_slot; p.part_o = part_o; p.part_ml = part_ml; p.out = (bf16*)out;
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
     p.num_kv_heads = num_kv_heads; p.max_chunks = max_chunks; p.status = status; p.slopes = slopes;
+    p.chunk = chunk; p.sinks = sinks;
     dim3 grid(max_chunks, num_kv_heads, num_seqs), merge_grid(num_heads, num_seqs);
 #define FRB_LAUNCH_DECODE(HD)                                                       \
     launch_dependent(attention_decode_mma_kernel<HD>, dim3(grid), dim3(128), 0, stream, p);                   \

@@ -86,6 +86,8 @@ struct AttnTcParams {
     float scale2;              // softmax scale * log2(e)
     int window, max_pages, num_heads, num_kv_heads;
     const float* slopes;       // SLOPED kernels: one slope per query head; key j's score is lowered by slope * (i - j)
+    int chunk;                 // 0, or a query sees only the keys of its own chunk of this many positions
+    const float* sinks;        // null, or one number per query head whose exponential joins the softmax's denominator
 };
 
 // grid (tile of 128 queries, head); the longest tiles of a sequence (its last ones) start first.
@@ -122,7 +124,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int q_len = p.seq_q_len[b], start = p.seq_start[b], tok0 = p.cu_q_len[b] + q0;
     const int* table = p.page_table + (size_t)p.seq_slot[b] * p.max_pages;
     const int last_key = start + min(q0 + AT_QUERIES - 1, q_len - 1);
-    const int first_key = p.window > 0 ? max(0, start + q0 - p.window + 1) : 0;
+    const int first_key = first_visible_key(start + q0, p.window, p.chunk);
     const int first_page = first_key / FRB_PAGE, num_pages = last_key / FRB_PAGE - first_page + 1;
     const int num_steps = (num_pages + AT_STEP_PAGES - 1) / AT_STEP_PAGES;     // a step: two pages, the last one maybe one
 
@@ -228,7 +230,7 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const uint32_t o_mine = lane_base + O_COL0 + 128 * half;
         const bool valid = q0 + row < q_len;
         const int hi = valid ? start + q0 + row : -1;
-        const int lo = (valid && p.window > 0) ? max(0, hi - p.window + 1) : 0;
+        const int lo = valid ? first_visible_key(hi, p.window, p.chunk) : 0;
         const float slope2 = SLOPED ? p.slopes[head] * 1.4426950408889634f : 0.f;
         float m_used = -INFINITY, l_sum = 0.f;
         bool ok = true, begun = false;
@@ -336,7 +338,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
         const float m_both = fmaxf(m_used, m_other);
         const float a_mine = m_used == -INFINITY ? 0.f : exp2f(m_used - m_both);
         const float a_other = m_other == -INFINITY ? 0.f : exp2f(m_other - m_both);
-        const float l_both = l_sum * a_mine + l_other * a_other;
+        float l_both = l_sum * a_mine + l_other * a_other;
+        if (p.sinks) l_both += exp2f(p.sinks[head] * 1.4426950408889634f - m_both);   // the sink: a term without a value
         const float inv = l_both > 0.f ? 1.0f / l_both : 0.f;
         // O_1 holds nothing if every step had one page (a sequence of at most 64 keys in reach)
         const float w0 = (half == 0 ? a_mine : a_other) * inv, w1 = num_pages > 1 ? (half == 0 ? a_other : a_mine) * inv : 0.f;
@@ -387,7 +390,8 @@ FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* 
                                      const int* page_table, int max_pages, const int* tile_seq, const int* tile_q0,
                                      int num_tiles, const int* seq_slot, const int* seq_start, const int* seq_q_len,
                                      const int* cu_q_len, void* out, int num_heads, int num_kv_heads, int head_dim, float scale,
-                                     int window, int* status, const float* slopes, cudaStream_t stream) {
+                                     int window, int* status, const float* slopes, int chunk, const float* sinks,
+                                     cudaStream_t stream) {
     if (num_tiles == 0) return 0;
     FRB_CHECK_ARG(head_dim == 64 || head_dim == 128, "tensor-core attention: head_dim %d is neither 64 nor 128", head_dim);
     FRB_CHECK_ARG(scale > 0.f, "tensor-core attention: a softmax scale of %g is not positive", (double)scale);
@@ -404,6 +408,7 @@ FRB_API int frb_attention_prefill_tc(const void* q, int num_tokens, const void* 
     p.seq_q_len = seq_q_len; p.cu_q_len = cu_q_len; p.out = (bf16*)out; p.status = status;
     p.scale2 = scale * 1.4426950408889634f; p.window = window; p.max_pages = max_pages; p.num_heads = num_heads;
     p.num_kv_heads = num_kv_heads; p.slopes = slopes;
+    p.chunk = chunk; p.sinks = sinks;
     const size_t smem = (size_t)AT_QUERIES * head_dim * 2 + (size_t)AT_STAGES * AT_STEP_PAGES * 2 * FRB_PAGE * head_dim * 2 + 1024;
     dim3 grid(num_tiles, num_heads);
 #define FRB_LAUNCH_TC(HD, SLOPED)                                                                                            \

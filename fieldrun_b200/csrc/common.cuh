@@ -95,6 +95,14 @@ inline void launch_dependent(void (*kernel)(Params...), dim3 grid, dim3 block, s
     launch_dependent_resident(1, kernel, grid, block, smem, stream, args...);
 }
 
+// The first key that the query at `pos` may see: with a window the last `window` keys, with chunks the keys of its own
+// chunk of `chunk` positions (chunks counted from position 0); 0 switches either off.
+__device__ __forceinline__ int first_visible_key(int pos, int window, int chunk) {
+    int lo = window > 0 ? max(0, pos - window + 1) : 0;
+    if (chunk > 0) lo = max(lo, pos / chunk * chunk);
+    return lo;
+}
+
 template <typename T> __device__ __forceinline__ float to_f32(T v);
 template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ float to_f32<bf16>(bf16 v) { return __bfloat162float(v); }

@@ -48,9 +48,9 @@ _SIGNATURES = {
     "frb_argmax_rows": "piippp",
     "frb_sample_floor": "piippppppp",
     "frb_gated_unit": "ppiii",
-    "frb_attention_decode_mma": "ppppipppppiiiifiipp",
-    "frb_attention_prefill_mma": "ppppippipppppiiifip",
-    "frb_attention_decode_tma": "pppipipppppiiiifiiipp",
+    "frb_attention_decode_mma": "ppppipppppiiiifiippip",
+    "frb_attention_prefill_mma": "ppppippipppppiiifipip",
+    "frb_attention_decode_tma": "pppipipppppiiiifiiippip",
     "frb_expert_gemm_mma": "pppppppiipiiiii",
     "frb_weight_stream": "pippppppiipiiiiiiip",
     "frb_route_plan_small": "ppiiiifipppppppp",
@@ -58,7 +58,7 @@ _SIGNATURES = {
     "frb_router_logits": "ppiiip",
     "frb_expert_gemm_tc": "pipippppiipiiipi",
     "frb_gather_rows_bf16": "pppii",
-    "frb_attention_prefill_tc": "pippipippipppppiiifipp",
+    "frb_attention_prefill_tc": "pippipippipppppiiifippip",
 }
 _CTYPE = {"p": _P, "i": _I, "f": _F, "l": _L}
 
@@ -716,24 +716,29 @@ ATTENTION_CHUNK = 256
 def attention_decode_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
                          seq_pos: torch.Tensor, seq_slot: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
                          out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
-                         window: Optional[int], max_chunks: int, slopes: Optional[torch.Tensor] = None) -> None:
+                         window: Optional[int], max_chunks: int, slopes: Optional[torch.Tensor] = None,
+                         chunk: Optional[int] = None, sinks: Optional[torch.Tensor] = None) -> None:
     """One token per sequence, bfloat16: keys split into chunks of 256 over blocks, merged in chunk order.
     ``slopes`` (float32 [num_heads], here and in the three kernels below): the score of key j for the query at
-    position i is lowered by slopes[h] * (i - j)."""
+    position i is lowered by slopes[h] * (i - j); ``chunk``: a query sees only the keys of its own chunk of that many
+    positions; ``sinks`` (float32 [num_heads]): exp(sinks[h]) joins the softmax's denominator."""
     _want_slopes(slopes, num_heads)
+    _want_slopes(sinks, num_heads)
     for t in (q, k_pages, v_pages, out):
         _want(t, torch.bfloat16, "tensor-core attention operands")
     _want(part_o, torch.float32, "partial outputs")
     _call("frb_attention_decode_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
           _ptr(seq_pos), _ptr(seq_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), q.shape[0], num_heads, num_kv_heads,
-          head_dim, float(scale), int(window or 0), max_chunks, _ptr(tc_status(q.device)), _ptr(slopes))
+          head_dim, float(scale), int(window or 0), max_chunks, _ptr(tc_status(q.device)), _ptr(slopes), int(chunk or 0),
+          _ptr(sinks))
 
 
 def _want_slopes(slopes: Optional[torch.Tensor], num_heads: int) -> None:
+    """A float32 number per query head (distance slopes, sinks), or None."""
     if slopes is not None:
-        _want(slopes, torch.float32, "distance slopes")
+        _want(slopes, torch.float32, "a number per head")
         if slopes.numel() != num_heads:
-            raise KernelError(f"{slopes.numel()} distance slopes for {num_heads} heads")
+            raise KernelError(f"{slopes.numel()} numbers for {num_heads} heads")
 
 
 _SM_COUNT: dict[int, int] = {}
@@ -766,7 +771,8 @@ def attention_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
                          seq_pos: torch.Tensor, seq_slot: torch.Tensor, part_o: torch.Tensor, part_ml: torch.Tensor,
                          out: torch.Tensor, *, num_heads: int, num_kv_heads: int, head_dim: int, scale: float,
                          window: Optional[int], max_chunks: int, chunks_per_block: Optional[int] = None,
-                         slopes: Optional[torch.Tensor] = None) -> None:
+                         slopes: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                         sinks: Optional[torch.Tensor] = None) -> None:
     """As :func:`attention_decode_mma` for head sizes 64 and 128, with the pages copied into shared memory by
     TMA through a ring of stages, which keeps far more bytes in flight; a block takes ``chunks_per_block``
     chunks (default: :func:`decode_chunks_per_block`)."""
@@ -774,26 +780,30 @@ def attention_decode_tma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
         _want(t, torch.bfloat16, "tensor-core attention operands")
     _want(part_o, torch.float32, "partial outputs")
     _want_slopes(slopes, num_heads)
+    _want_slopes(sinks, num_heads)
     if chunks_per_block is None:
         chunks_per_block = decode_chunks_per_block(q.shape[0], num_kv_heads, max_chunks, sm_count(q.device))
     _call("frb_attention_decode_tma", _ptr(q), _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(page_table),
           page_table.shape[1], _ptr(seq_pos), _ptr(seq_slot), _ptr(part_o), _ptr(part_ml), _ptr(out), q.shape[0], num_heads,
           num_kv_heads, head_dim, float(scale), int(window or 0), max_chunks, int(chunks_per_block),
-          _ptr(tc_status(q.device)), _ptr(slopes))
+          _ptr(tc_status(q.device)), _ptr(slopes), int(chunk or 0), _ptr(sinks))
 
 
 def attention_prefill_mma(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.Tensor, page_table: torch.Tensor,
                           tile_seq: torch.Tensor, tile_q0: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor,
                           seq_q_len: torch.Tensor, cu_q_len: torch.Tensor, out: torch.Tensor, *, num_heads: int,
                           num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-                          slopes: Optional[torch.Tensor] = None) -> None:
+                          slopes: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                          sinks: Optional[torch.Tensor] = None) -> None:
     """Many tokens per sequence, bfloat16: tiles of 16 queries, causal, blockwise over the cache pages."""
     for t in (q, k_pages, v_pages, out):
         _want(t, torch.bfloat16, "tensor-core attention operands")
     _want_slopes(slopes, num_heads)
+    _want_slopes(sinks, num_heads)
     _call("frb_attention_prefill_mma", _ptr(q), _ptr(k_pages), _ptr(v_pages), _ptr(page_table), page_table.shape[1],
           _ptr(tile_seq), _ptr(tile_q0), tile_seq.numel(), _ptr(seq_slot), _ptr(seq_start), _ptr(seq_q_len),
-          _ptr(cu_q_len), _ptr(out), num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), _ptr(slopes))
+          _ptr(cu_q_len), _ptr(out), num_heads, num_kv_heads, head_dim, float(scale), int(window or 0), _ptr(slopes),
+          int(chunk or 0), _ptr(sinks))
 
 
 def expert_gemm_mma(w: torch.Tensor, x: torch.Tensor, x_rows: Optional[torch.Tensor], tile_expert: torch.Tensor,
@@ -981,16 +991,18 @@ def attention_prefill_tc(q: torch.Tensor, k_pages: torch.Tensor, v_pages: torch.
                          tile_seq: torch.Tensor, tile_q0: torch.Tensor, seq_slot: torch.Tensor, seq_start: torch.Tensor,
                          seq_q_len: torch.Tensor, cu_q_len: torch.Tensor, out: torch.Tensor, *, num_heads: int,
                          num_kv_heads: int, head_dim: int, scale: float, window: Optional[int],
-                         slopes: Optional[torch.Tensor] = None) -> None:
+                         slopes: Optional[torch.Tensor] = None, chunk: Optional[int] = None,
+                         sinks: Optional[torch.Tensor] = None) -> None:
     """Many tokens per sequence on tcgen05 tensor cores: tiles of 128 queries of one head (bfloat16, head sizes
     64 and 128)."""
     for t in (q, k_pages, v_pages, out):
         _want(t, torch.bfloat16, "tensor-core attention operands")
     _want_slopes(slopes, num_heads)
+    _want_slopes(sinks, num_heads)
     _call("frb_attention_prefill_tc", _ptr(q), q.shape[0], _ptr(k_pages), _ptr(v_pages), k_pages.shape[0], _ptr(page_table),
           page_table.shape[1], _ptr(tile_seq), _ptr(tile_q0), tile_seq.numel(), _ptr(seq_slot), _ptr(seq_start),
           _ptr(seq_q_len), _ptr(cu_q_len), _ptr(out), num_heads, num_kv_heads, head_dim, float(scale), int(window or 0),
-          _ptr(tc_status(q.device)), _ptr(slopes))
+          _ptr(tc_status(q.device)), _ptr(slopes), int(chunk or 0), _ptr(sinks))
 
 
 def wait_probe(device, limit_cycles: int = 100_000) -> int:

@@ -179,11 +179,11 @@ class GQAAttention(Mixer):
     def attend(self, ctx, q: torch.Tensor, line: LineView, out: torch.Tensor, gate: Optional[torch.Tensor] = None) -> None:
         """Tensor-core kernels for bfloat16 and head sizes of 32, 64, 96 or 128 (tcgen05 for prompts with head
         sizes 64 and 128, mma.sync otherwise), keys and values of one size; the general kernel for everything else.
-        All of them take the distance slopes; chunks, sinks and head gates go through the general kernel."""
+        All of them take the distance slopes, chunks and sinks; the general kernel applies the head gates itself, after
+        the others a small kernel does."""
         common = dict(num_heads=self.num_heads, num_kv_heads=self.num_kv_heads, head_dim=self.head_dim,
-                      scale=self.softmax_scale, window=self.window, slopes=self.slopes)
-        plain = self.chunk is None and self.sinks is None and gate is None
-        if plain and self.value_dim == self.head_dim and self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
+                      scale=self.softmax_scale, window=self.window, slopes=self.slopes, chunk=self.chunk, sinks=self.sinks)
+        if self.value_dim == self.head_dim and self.dtype == torch.bfloat16 and self.head_dim in ops.MMA_HEAD_DIMS:
             if ctx.is_decode and self.num_heads // self.num_kv_heads <= 16:
                 chunks = (ctx.max_kv_len + ops.ATTENTION_CHUNK - 1) // ops.ATTENTION_CHUNK
                 part_o = ctx.buffer("attention.part_o", (ctx.num_seqs, self.num_heads, chunks, self.head_dim), torch.float32)
@@ -201,9 +201,11 @@ class GQAAttention(Mixer):
                 tile_seq, tile_q0 = ctx.query_tiles(16)
                 ops.attention_prefill_mma(q, line.keys, line.values, line.page_table, tile_seq, tile_q0, ctx.seq_slot,
                                           ctx.seq_start, ctx.seq_q_len, ctx.cu_q_len, out, **common)
+            if gate is not None:
+                ops.head_gate(out, gate, self.num_heads, self.value_dim)
             return
         ops.attention_generic(q, line.keys, line.values, line.page_table, ctx.tok_pos, ctx.tok_slot, out,
-                              v_dim=self.value_dim, chunk=self.chunk, sinks=self.sinks, gate=gate, **common)
+                              v_dim=self.value_dim, gate=gate, **common)
 
 
 register_part("mixer", "gqa_attention", GQAAttention, replace=True)

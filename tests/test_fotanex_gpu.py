@@ -346,6 +346,74 @@ def test_a_key_just_outside_the_chunk_gets_nothing_and_one_just_inside_gets_near
         close(f64(out), want, KERNEL_TOL[dtype], "chunk edge")
 
 
+def chunked_case(rng, heads, kv_heads, dim, seqs, chunk):
+    """Sequences (start, new tokens): keys and values of start + new positions in scrambled pages, a query for each new
+    token, a sink per head, and what the plain implementation makes of them.  One early key of the last sequence is
+    made to stand out: it counts only for the queries of its own chunk."""
+    lengths = [start + n for start, n in seqs]
+    keys, values, kc, vc, table = scrambled_pages(rng, lengths, kv_heads, dim, dim, "bfloat16")
+    rows = [(s, start + i) for s, (start, n) in enumerate(seqs) for i in range(n)]
+    q = rounded(rng.normal(size=(len(rows), heads, dim)), "bfloat16")
+    last = len(seqs) - 1
+    far = min(5, lengths[last] - 1)
+    keys[last][far] = rounded(q[len(rows) - 1, ::heads // kv_heads] * 3.0, "bfloat16")
+    values[last][far] = 9.0
+    lay_into_pages(keys, values, kc, vc, table)
+    sink = rng.normal(1.0, 2.0, heads)
+    want = np.stack([pf.attend_in_chunks(q[r:r + 1], keys[s], values[s], sink.astype(np.float32), None, 0.2, chunk, positions=[p])[0].reshape(-1)
+                     for r, (s, p) in enumerate(rows)])
+    return dict(q=dev(q.reshape(len(rows), heads * dim), torch.bfloat16), kc=dev(kc, torch.bfloat16), vc=dev(vc, torch.bfloat16),
+                table=dev(table), sink=f32(sink), rows=rows, want=want)
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim", [(6, 1, 128), (8, 8, 64), (32, 2, 32), (12, 2, 96), (4, 2, 64)])
+@pytest.mark.parametrize("chunk", [64, 100, 640])
+@pytest.mark.parametrize("kernel", ["attention_decode_mma", "attention_decode_tma"])
+def test_one_token_attention_on_tensor_cores_in_chunks_with_sinks(heads, kv_heads, dim, chunk, kernel):
+    if kernel == "attention_decode_tma" and dim not in (64, 128):
+        pytest.skip("the TMA kernel takes head sizes 64 and 128")
+    rng = np.random.default_rng(dim + heads + chunk)
+    c = chunked_case(rng, heads, kv_heads, dim, [(999, 1), (256, 1), (63, 1), (0, 1), (512, 1), (chunk, 1), (chunk - 1, 1), (2 * chunk + 3, 1)], chunk)
+    positions = np.array([p for _, p in c["rows"]], dtype=np.int32)
+    chunks = (int(positions.max()) + 256) // 256
+    n = len(positions)
+    part_o = torch.full((n, heads, chunks, dim), float("nan"), dtype=torch.float32, device=DEV)
+    part_ml = torch.full((n, heads, chunks, 2), float("nan"), dtype=torch.float32, device=DEV)
+    for extra in ([{}] if kernel == "attention_decode_mma" else [{}, {"chunks_per_block": 2}, {"chunks_per_block": 4}]):
+        out = torch.full_like(c["q"], 7.0)
+        getattr(ops(), kernel)(c["q"], c["kc"], c["vc"], c["table"], dev(positions), dev(np.arange(n, dtype=np.int32)), part_o,
+                               part_ml, out, num_heads=heads, num_kv_heads=kv_heads, head_dim=dim, scale=0.2, window=None,
+                               max_chunks=chunks, chunk=chunk, sinks=c["sink"], **extra)
+        ops().tc_status_check(DEV)
+        close(f64(out), c["want"], 1.2e-2, f"{kernel} {extra}")
+
+
+@pytest.mark.parametrize("heads,kv_heads,dim", [(6, 1, 128), (4, 4, 64), (8, 2, 32), (6, 2, 96)])
+@pytest.mark.parametrize("chunk", [64, 100, 128, 640])
+@pytest.mark.parametrize("kernel", ["attention_prefill_mma", "attention_prefill_tc"])
+def test_many_token_attention_on_tensor_cores_in_chunks_with_sinks_and_the_head_gate(heads, kv_heads, dim, chunk, kernel):
+    if kernel == "attention_prefill_tc" and dim not in (64, 128):
+        pytest.skip("the tcgen05 kernel takes head sizes 64 and 128")
+    rng = np.random.default_rng(3 * dim + heads + chunk)
+    seqs = [(0, 300), (130, 17), (0, 1), (63, 200), (500, 129), (0, 700)]
+    c = chunked_case(rng, heads, kv_heads, dim, seqs, chunk)
+    tile = 128 if kernel == "attention_prefill_tc" else 16
+    tile_seq = np.concatenate([np.full((n + tile - 1) // tile, b) for b, (_, n) in enumerate(seqs)]).astype(np.int32)
+    tile_q0 = np.concatenate([np.arange(0, n, tile) for _, n in seqs]).astype(np.int32)
+    q_lens = np.array([n for _, n in seqs], dtype=np.int32)
+    cu = np.concatenate([[0], np.cumsum(q_lens)]).astype(np.int32)
+    out = torch.full_like(c["q"], 7.0)
+    getattr(ops(), kernel)(c["q"], c["kc"], c["vc"], c["table"], dev(tile_seq), dev(tile_q0), dev(np.arange(len(seqs), dtype=np.int32)),
+                           dev(np.array([s for s, _ in seqs], dtype=np.int32)), dev(q_lens), dev(cu), out, num_heads=heads,
+                           num_kv_heads=kv_heads, head_dim=dim, scale=0.2, window=None, chunk=chunk, sinks=c["sink"])
+    ops().tc_status_check(DEV)
+    close(f64(out), c["want"], 1.2e-2, kernel)
+    gate = rng.normal(size=(len(c["rows"]), heads))
+    ops().head_gate(out, f32(gate), heads, dim)
+    gated = c["want"].reshape(len(c["rows"]), heads, dim) * pf.sigmoid(gate.astype(np.float32))[:, :, None]
+    close(f64(out), gated.reshape(len(c["rows"]), -1), 1.6e-2, "head gate")
+
+
 @pytest.mark.parametrize("experts,top", [(8, 3), (5, 1), (4, 4), (40, 6), (300, 2)])
 def test_softmax_scores_and_the_floor_under_their_sum(experts, top):
     rng = np.random.default_rng(experts)
