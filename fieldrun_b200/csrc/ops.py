@@ -35,8 +35,9 @@ _SIGNATURES = {
     "frb_add_row_vector": "pppii",
     "frb_head_gate": "pipiiii",
     "frb_causal_conv": "piippppppppllppiiiii",
-    "frb_selective_scan": "piippiiippppppppllpiiii",
-    "frb_gated_recurrence": "piippppppppppllpiiiiif",
+    "frb_selective_scan": "piippiiipppppppllpiiii",
+    "frb_softplus_bias": "ppii",
+    "frb_gated_recurrence": "piipppppppppppllpiiiiif",
     "frb_state_space_scan": "piiipiiipppppppllpiiiii",
     "frb_group_rms_norm": "pppiiiif",
     "frb_gla_scan": "piiiiiipipppppppiiiiiifffppppippi",
@@ -78,7 +79,7 @@ _ENTRY_GROUPS = {
                 "frb_router_small", "frb_router_logits"),
     "products": ("frb_expert_gemm_tc", "frb_gather_rows_bf16"),
     "recurrent": ("frb_gla_scan",),
-    "scans": ("frb_causal_conv", "frb_selective_scan", "frb_gated_recurrence", "frb_state_space_scan", "frb_group_rms_norm"),
+    "scans": ("frb_causal_conv", "frb_softplus_bias", "frb_selective_scan", "frb_gated_recurrence", "frb_state_space_scan", "frb_group_rms_norm"),
     "extras": ("frb_wait_probe",),
 }
 _GROUP_OF = {entry: group for group, entries in _ENTRY_GROUPS.items() for entry in entries}
@@ -159,7 +160,7 @@ def _stream() -> int:
 
 
 _LAUNCHES = 0
-_KERNELS_PER_CALL = {"frb_sample_floor": 3, "frb_argmax_rows": 2, "frb_expert_plan": 3, "frb_attention_decode_mma": 2, "frb_attention_decode_tma": 2}
+_KERNELS_PER_CALL = {"frb_gated_recurrence": 2, "frb_sample_floor": 3, "frb_argmax_rows": 2, "frb_expert_plan": 3, "frb_attention_decode_mma": 2, "frb_attention_decode_tma": 2}
 
 
 def launches() -> int:
@@ -445,25 +446,30 @@ def selective_scan(xz: torch.Tensor, z_offset: int, x: torch.Tensor, low: torch.
                    dt: torch.Tensor, dt_bias: torch.Tensor, a_log: torch.Tensor, d: torch.Tensor, ctx, state: torch.Tensor,
                    state_offset: int, out: torch.Tensor) -> None:
     """S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n, y_c = sum_n S[c, n] C_n + D_c x_c, out = y silu(z), with
-    dt = softplus(``dt`` + ``dt_bias``) and A = -exp(``a_log``); all inputs float32."""
+    dt = softplus(``dt`` + ``dt_bias``) (made in place, by a kernel of its own) and A = -exp(``a_log``); all inputs
+    float32."""
     for t in (xz, x, low, dt, dt_bias, a_log, d):
         _want(t, torch.float32, "selective_scan's inputs")
     inner, n = a_log.shape
+    _call("frb_softplus_bias", _ptr(dt), _ptr(dt_bias), dt.shape[0], inner)
     _call("frb_selective_scan", _ptr(xz), xz.shape[1], int(z_offset), _ptr(x), _ptr(low), low.shape[1], int(b_offset),
-          int(c_offset), _ptr(dt), _ptr(dt_bias), _ptr(a_log), _ptr(d), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
+          int(c_offset), _ptr(dt), _ptr(a_log), _ptr(d), _ptr(ctx.seq_slot), _ptr(ctx.seq_start),
           _ptr(ctx.cu_q_len), *_state_place(state, state_offset), _ptr(out), _code(out.dtype), ctx.num_seqs, inner, n)
 
 
 def gated_recurrence(yx: torch.Tensor, y_offset: int, y_bias: Optional[torch.Tensor], u: torch.Tensor, gates: torch.Tensor,
                      a_bias: torch.Tensor, i_bias: torch.Tensor, lam: torch.Tensor, ctx, state: torch.Tensor, state_offset: int,
-                     out: torch.Tensor, *, block_width: int, gate_constant: float) -> None:
+                     out: torch.Tensor, *, block_width: int, gate_constant: float, prepared: torch.Tensor) -> None:
     """a = exp(-gate_constant * sigmoid(r + a_bias) * softplus(lam)), S <- a S + sqrt(1 - a^2) sigmoid(i + i_bias) u,
-    out = S * gelu_tanh(y + y_bias); ``gates`` float32 [blocks, T, 2 * block_width] holds r then i of every block."""
+    out = S * gelu_tanh(y + y_bias); ``gates`` float32 [blocks, T, 2 * block_width] holds r then i of every block;
+    ``prepared``: float32 scratch of 3 * T * channels elements (what does not depend on the state is made first)."""
     for t in (yx, u, gates, a_bias, i_bias, lam):
         _want(t, torch.float32, "gated_recurrence's inputs")
     channels = u.shape[1]
+    if prepared.dtype != torch.float32 or prepared.numel() < 3 * u.numel():
+        raise KernelError("gated_recurrence needs float32 scratch of three times the rows")
     _call("frb_gated_recurrence", _ptr(yx), yx.shape[1], int(y_offset), _ptr(y_bias), _ptr(u), _ptr(gates), _ptr(a_bias),
-          _ptr(i_bias), _ptr(lam), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.cu_q_len),
+          _ptr(i_bias), _ptr(lam), _ptr(prepared), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.cu_q_len),
           *_state_place(state, state_offset), _ptr(out), _code(out.dtype), ctx.num_seqs, u.shape[0], channels, int(block_width),
           float(gate_constant))
 

@@ -39,6 +39,13 @@ __device__ __forceinline__ float* state_at(const StatePlace& s, int slot, int co
 __device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+// exp(x) - 1 for x <= 0 (a decay less one): a short series where the result is small, else the fast exponential,
+// whose error of a few 1e-7 of the decay then matters as little as the rounding of the state itself.
+__device__ __forceinline__ float decay_less_one(float x) {
+    const float series = x * fmaf(x * 0.5f, fmaf(x * (1.0f / 3.0f), fmaf(x * 0.25f, fmaf(x, 0.2f, 1.0f), 1.0f), 1.0f), 1.0f);
+    return x > -0.0625f ? series : __expf(x) - 1.0f;
+}
+
 __device__ __forceinline__ float gelu_tanh_f(float v) {
     return 0.5f * v * (1.0f + tanhf(0.7978845608028654f * (v + 0.044715f * v * v * v)));
 }
@@ -58,69 +65,89 @@ struct ConvParams {
     float* out32;            // [T, C]
     void* out_typed;         // null, or [T, C] in the model dtype
     int in_stride, in_offset, channels, taps_count, activation, num_rows;
+    int rows_per_thread;     // CONV_ROWS for a step of many rows, 1 for a step of few (one token a sequence)
 };
 
 __device__ __forceinline__ float conv_activation(float v, int activation) { return activation == 1 ? silu_f(v) : v; }
 
-// A thread per (row, channel).  The thread of a sequence's first new row does all that touches the state: the
-// outputs of the first K-1 rows (the only ones that see inputs from before the step) and the new state.
+#define CONV_ROWS 8          // rows of the step that one thread takes, one after the other, for its channel
+
+// A thread takes CONV_ROWS rows of the step for one channel and keeps the inputs it has seen in registers (right
+// aligned: the newest last), so that a row costs one load.  The row that is a sequence's first new one does all that
+// touches the state: the outputs of the first K-1 rows (the only ones that see inputs from before the step) and the
+// new state; rows 1 .. K-2 of a sequence are therefore skipped wherever they fall.
 template <typename OutT>
 __global__ void __launch_bounds__(128) causal_conv_kernel(ConvParams p) {
     after_previous_kernel();
     const int c = blockIdx.y * 128 + threadIdx.x;
-    const int r = blockIdx.x;
     if (c >= p.channels) return;
     const int K = p.taps_count;
-    const int b = p.tok_seq[r];
-    const int row0 = p.seq.cu_q_len[b], n = p.seq.cu_q_len[b + 1] - row0;
-    const int i = r - row0;
-    if (i > 0 && i < K - 1) return;
-    float w[CONV_MAX_TAPS];
+    float w[CONV_MAX_TAPS];                    // right aligned like the window: w[MAX - K + k] is tap k
 #pragma unroll
-    for (int k = 0; k < CONV_MAX_TAPS; ++k) w[k] = k < K ? p.taps[(size_t)c * K + k] : 0.f;
+    for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = j >= CONV_MAX_TAPS - K ? p.taps[(size_t)c * K + j - (CONV_MAX_TAPS - K)] : 0.f;
     const float bias = p.bias ? p.bias[c] : 0.f, in_bias = p.in_bias ? p.in_bias[c] : 0.f;
     const float* in = p.in + p.in_offset + c;
     OutT* typed = (OutT*)p.out_typed;
-    if (i >= K - 1) {
-        float acc = bias;
+    float win[CONV_MAX_TAPS];
+    bool have = false;                         // win holds the inputs of the row before this one
+    const int r_end = min(p.num_rows, (int)(blockIdx.x + 1) * p.rows_per_thread);
+    for (int r = blockIdx.x * p.rows_per_thread; r < r_end; ++r) {
+        const int b = p.tok_seq[r];
+        const int row0 = p.seq.cu_q_len[b];
+        const int i = r - row0;
+        if (i >= K - 1) {
+            if (have) {
 #pragma unroll
-        for (int k = 0; k < CONV_MAX_TAPS; ++k)
-            if (k < K) acc += w[k] * (in[(size_t)(r - (K - 1) + k) * p.in_stride] + in_bias);
-        acc = conv_activation(acc, p.activation);
-        p.out32[(size_t)r * p.channels + c] = acc;
-        if (typed) typed[(size_t)r * p.channels + c] = from_f32<OutT>(acc);
-        return;                                 // with K == 1 there is no state and every row ends here
-    }
-    // i == 0
-    const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
-    const float* old_tail = state_at(p.state, slot, start & 1);
-    float* new_tail = state_at(p.state, slot, (start + n) & 1);
-    // hist[m], m < K-1: the inputs before the step; hist[K-1+j]: the step's own input j, for the rows handled here
-    float hist[2 * CONV_MAX_TAPS];
+                for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) win[j] = win[j + 1];
+                win[CONV_MAX_TAPS - 1] = in[(size_t)r * p.in_stride] + in_bias;
+            } else {
 #pragma unroll
-    for (int m = 0; m < CONV_MAX_TAPS; ++m) hist[m] = m < K - 1 ? old_tail[(size_t)m * p.channels + c] : 0.f;
-    const int own = min(n, K - 1);
+                for (int j = 0; j < CONV_MAX_TAPS; ++j)
+                    win[j] = j >= CONV_MAX_TAPS - K ? in[(size_t)(r - (CONV_MAX_TAPS - 1 - j)) * p.in_stride] + in_bias : 0.f;
+                have = true;
+            }
+            float acc = bias;
 #pragma unroll
-    for (int j = 0; j < CONV_MAX_TAPS; ++j)
-        hist[CONV_MAX_TAPS + j] = j < own ? in[(size_t)(row0 + j) * p.in_stride] + in_bias : 0.f;
-    for (int j = 0; j < own; ++j) {
-        float acc = bias;
-        for (int k = 0; k < K; ++k) {
-            const int at = j - (K - 1) + k;                       // index among the step's inputs; negative: before it
-            const float v = at >= 0 ? hist[CONV_MAX_TAPS + at] : hist[K - 1 + at];
-            acc += w[k] * v;
+            for (int j = 0; j < CONV_MAX_TAPS; ++j) acc = fmaf(w[j], win[j], acc);
+            acc = conv_activation(acc, p.activation);
+            p.out32[(size_t)r * p.channels + c] = acc;
+            if (typed) typed[(size_t)r * p.channels + c] = from_f32<OutT>(acc);
+            continue;                           // with K == 1 there is no state and every row ends here
         }
-        acc = conv_activation(acc, p.activation);
-        p.out32[(size_t)(row0 + j) * p.channels + c] = acc;
-        if (typed) typed[(size_t)(row0 + j) * p.channels + c] = from_f32<OutT>(acc);
-    }
-    for (int m = 0; m < K - 1; ++m) {
-        const int at = n - (K - 1) + m;                           // the step's input that becomes entry m of the new state
-        float v;
-        if (at < 0) v = hist[K - 1 + at];
-        else if (at < own) v = hist[CONV_MAX_TAPS + at];
-        else v = in[(size_t)(row0 + at) * p.in_stride] + in_bias;
-        new_tail[(size_t)m * p.channels + c] = v;
+        have = false;
+        if (i > 0) continue;
+        // i == 0
+        const int n = p.seq.cu_q_len[b + 1] - row0;
+        const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
+        const float* old_tail = state_at(p.state, slot, start & 1);
+        float* new_tail = state_at(p.state, slot, (start + n) & 1);
+        // hist[m], m < K-1: the inputs before the step; hist[MAX + j]: the step's own input j, for the rows handled here
+        float hist[2 * CONV_MAX_TAPS];
+#pragma unroll
+        for (int m = 0; m < CONV_MAX_TAPS; ++m) hist[m] = m < K - 1 ? old_tail[(size_t)m * p.channels + c] : 0.f;
+        const int own = min(n, K - 1);
+#pragma unroll
+        for (int j = 0; j < CONV_MAX_TAPS; ++j)
+            hist[CONV_MAX_TAPS + j] = j < own ? in[(size_t)(row0 + j) * p.in_stride] + in_bias : 0.f;
+        for (int j = 0; j < own; ++j) {
+            float acc = bias;
+            for (int k = 0; k < K; ++k) {
+                const int at = j - (K - 1) + k;                       // index among the step's inputs; negative: before it
+                const float v = at >= 0 ? hist[CONV_MAX_TAPS + at] : hist[K - 1 + at];
+                acc = fmaf(p.taps[(size_t)c * K + k], v, acc);
+            }
+            acc = conv_activation(acc, p.activation);
+            p.out32[(size_t)(row0 + j) * p.channels + c] = acc;
+            if (typed) typed[(size_t)(row0 + j) * p.channels + c] = from_f32<OutT>(acc);
+        }
+        for (int m = 0; m < K - 1; ++m) {
+            const int at = n - (K - 1) + m;                           // the step's input that becomes entry m of the new state
+            float v;
+            if (at < 0) v = hist[K - 1 + at];
+            else if (at < own) v = hist[CONV_MAX_TAPS + at];
+            else v = in[(size_t)(row0 + at) * p.in_stride] + in_bias;
+            new_tail[(size_t)m * p.channels + c] = v;
+        }
     }
 }
 
@@ -139,7 +166,8 @@ FRB_API int frb_causal_conv(const float* in, int in_stride, int in_offset, const
     p.out32 = out32; p.out_typed = out_typed; p.in_stride = in_stride; p.in_offset = in_offset; p.channels = channels;
     p.taps_count = taps_count; p.activation = activation; p.num_rows = num_rows;
     FRB_CHECK_ARG((channels + 127) / 128 <= 65535, "causal_conv: %d channels exceed the grid", channels);
-    dim3 grid(num_rows, (channels + 127) / 128);
+    p.rows_per_thread = num_rows >= 2048 ? CONV_ROWS : 1;
+    dim3 grid((num_rows + p.rows_per_thread - 1) / p.rows_per_thread, (channels + 127) / 128);
     FRB_DISPATCH_DTYPE(typed_dtype, OutT, {
         launch_dependent(causal_conv_kernel<OutT>, grid, dim3(128), 0, stream, p);
     });
@@ -148,15 +176,30 @@ FRB_API int frb_causal_conv(const float* in, int in_stride, int in_offset, const
 
 // ---------------------------------------------------------------------------------------------------- selective_scan
 
-#define SEL_REGS 16          // state elements of one channel that a thread keeps
 #define SEL_BLOCK 128
+
+// x <- softplus(x + bias), row by row: the step sizes of the selective scan, made once for all the lanes that share them
+__global__ void __launch_bounds__(256) softplus_bias_kernel(float* __restrict__ x, const float* __restrict__ bias, int width) {
+    after_previous_kernel();
+    const int c = blockIdx.y * 256 + threadIdx.x;
+    if (c < width) {
+        const size_t i = (size_t)blockIdx.x * width + c;
+        x[i] = softplus_f(x[i] + bias[c]);
+    }
+}
+
+FRB_API int frb_softplus_bias(float* x, const float* bias, int num_rows, int width, cudaStream_t stream) {
+    if (num_rows == 0) return 0;
+    FRB_CHECK_ARG((width + 255) / 256 <= 65535, "softplus_bias: rows of %d exceed the grid", width);
+    launch_dependent(softplus_bias_kernel, dim3(num_rows, (width + 255) / 256), dim3(256), 0, stream, x, bias, width);
+    FRB_RETURN_LAUNCH("softplus_bias");
+}
 
 struct SelScanParams {
     const float* xz;         // [T, xz_stride]: z of channel c at z_offset + c
     const float* x;          // [T, inner]: the convolution's output
     const float* low;        // [T, low_stride]: B at b_offset, C at c_offset
-    const float* dt;         // [T, inner]: the step size before bias and softplus
-    const float* dt_bias;    // [inner]
+    const float* dt;         // [T, inner]: the step size (after bias and softplus)
     const float* a_log;      // [inner, N]
     const float* d;          // [inner]
     SeqTables seq;
@@ -165,8 +208,10 @@ struct SelScanParams {
     int xz_stride, z_offset, low_stride, b_offset, c_offset, inner, N, split;
 };
 
-// A channel's N state elements lie on `split` neighbouring lanes (a power of two), SEL_REGS each.
-template <typename OutT>
+// A channel's N state elements lie on `split` neighbouring lanes (a power of two), REGS each.  Few elements a lane
+// (REGS 2 or 4) spread a prompt of few sequences over the whole device; many (16) spare the lanes' additions where a
+// step has channels enough.
+template <typename OutT, int REGS>
 __global__ void __launch_bounds__(SEL_BLOCK) selective_scan_kernel(SelScanParams p) {
     extern __shared__ float sm[];
     after_previous_kernel();
@@ -180,16 +225,16 @@ __global__ void __launch_bounds__(SEL_BLOCK) selective_scan_kernel(SelScanParams
     const bool live = c < p.inner;
     const int row0 = p.seq.cu_q_len[b], n_tok = p.seq.cu_q_len[b + 1] - row0;
     const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
-    const int n0 = part * SEL_REGS;
-    float S[SEL_REGS], A[SEL_REGS];
+    const int n0 = part * REGS;
+    float S[REGS], A[REGS];
     const float* s_in = state_at(p.state, slot, start & 1);
 #pragma unroll
-    for (int i = 0; i < SEL_REGS; ++i) {
+    for (int i = 0; i < REGS; ++i) {
         const bool has = live && n0 + i < N;
         S[i] = has ? s_in[(size_t)c * N + n0 + i] : 0.f;
         A[i] = has ? -expf(p.a_log[(size_t)c * N + n0 + i]) : 0.f;
     }
-    const float bias = live ? p.dt_bias[c] : 0.f, dskip = live ? p.d[c] : 0.f;
+    const float dskip = live ? p.d[c] : 0.f;
     OutT* out = (OutT*)p.out;
     for (int t0 = 0; t0 < n_tok; t0 += SCAN_TOKENS) {
         const int count = min(SCAN_TOKENS, n_tok - t0);
@@ -213,14 +258,14 @@ __global__ void __launch_bounds__(SEL_BLOCK) selective_scan_kernel(SelScanParams
 #pragma unroll
         for (int t = 0; t < SCAN_TOKENS; ++t) {
             if (t < count) {
-                const float step = softplus_f(dtv[t] + bias);
+                const float step = dtv[t];
                 const float sx = step * xv[t];
                 float y = 0.f;
 #pragma unroll
-                for (int i = 0; i < SEL_REGS; ++i) {
+                for (int i = 0; i < REGS; ++i) {
                     if (n0 + i < N) {
-                        S[i] = fmaf(expm1f(step * A[i]), S[i], S[i]) + sx * s_b[t * N + n0 + i];
-                        y += S[i] * s_c[t * N + n0 + i];
+                        S[i] = fmaf(decay_less_one(step * A[i]), S[i], S[i]) + sx * s_b[t * N + n0 + i];
+                        y = fmaf(S[i], s_c[t * N + n0 + i], y);
                     }
                 }
                 for (int o = 1; o < split; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
@@ -232,24 +277,35 @@ __global__ void __launch_bounds__(SEL_BLOCK) selective_scan_kernel(SelScanParams
     if (live) {
         float* s_out = state_at(p.state, slot, (start + n_tok) & 1);
 #pragma unroll
-        for (int i = 0; i < SEL_REGS; ++i)
+        for (int i = 0; i < REGS; ++i)
             if (n0 + i < N) s_out[(size_t)c * N + n0 + i] = S[i];
     }
 }
 
+static inline int split_for(int N, int regs) {
+    int split = 1;
+    while (split * regs < N) split <<= 1;
+    return split;
+}
+
 FRB_API int frb_selective_scan(const float* xz, int xz_stride, int z_offset, const float* x, const float* low, int low_stride,
-                               int b_offset, int c_offset, const float* dt, const float* dt_bias, const float* a_log,
-                               const float* d, const int* seq_slot, const int* seq_start, const int* cu_q_len, float* state,
+                               int b_offset, int c_offset, const float* dt, const float* a_log, const float* d,
+                               const int* seq_slot, const int* seq_start, const int* cu_q_len, float* state,
                                long long copy_floats, long long state_offset, void* out, int out_dtype, int num_seqs, int inner,
                                int N, cudaStream_t stream) {
     if (num_seqs == 0) return 0;
-    int split = 1;
-    while (split * SEL_REGS < N) split <<= 1;
-    FRB_CHECK_ARG(split <= 32, "selective_scan: a state of %d per channel is more than the kernel's %d", N, 32 * SEL_REGS);
+    FRB_CHECK_ARG(N >= 1 && N <= 512, "selective_scan: a state of %d per channel is outside 1..512", N);
     FRB_CHECK_ARG(num_seqs <= 65535, "selective_scan: %d sequences exceed the grid", num_seqs);
+    // channels enough for the device with 16 elements a lane?  else 2 or 4 a lane, whichever leaves fewer lanes idle
+    int regs = 16;
+    if ((long long)num_seqs * inner * split_for(N, 16) < 128 * 1024 || split_for(N, 16) > 32) {
+        regs = split_for(N, 2) * 2 - N <= split_for(N, 4) * 4 - N && split_for(N, 2) <= 32 ? 2 : 4;
+        if (split_for(N, regs) > 32) regs = 16;
+    }
+    const int split = split_for(N, regs);
     SelScanParams p;
     p.xz = xz; p.xz_stride = xz_stride; p.z_offset = z_offset; p.x = x; p.low = low; p.low_stride = low_stride;
-    p.b_offset = b_offset; p.c_offset = c_offset; p.dt = dt; p.dt_bias = dt_bias; p.a_log = a_log; p.d = d;
+    p.b_offset = b_offset; p.c_offset = c_offset; p.dt = dt; p.a_log = a_log; p.d = d;
     p.seq = SeqTables{seq_slot, seq_start, cu_q_len};
     p.state = StatePlace{state, copy_floats, state_offset};
     p.out = out; p.inner = inner; p.N = N; p.split = split;
@@ -257,7 +313,9 @@ FRB_API int frb_selective_scan(const float* xz, int xz_stride, int z_offset, con
     dim3 grid((inner + per_block - 1) / per_block, num_seqs);
     const size_t smem = (size_t)2 * SCAN_TOKENS * N * sizeof(float);
     FRB_DISPATCH_DTYPE(out_dtype, OutT, {
-        launch_dependent(selective_scan_kernel<OutT>, grid, dim3(SEL_BLOCK), smem, stream, p);
+        if (regs == 2) launch_dependent(selective_scan_kernel<OutT, 2>, grid, dim3(SEL_BLOCK), smem, stream, p);
+        else if (regs == 4) launch_dependent(selective_scan_kernel<OutT, 4>, grid, dim3(SEL_BLOCK), smem, stream, p);
+        else launch_dependent(selective_scan_kernel<OutT, 16>, grid, dim3(SEL_BLOCK), smem, stream, p);
     });
     FRB_RETURN_LAUNCH("selective_scan");
 }
@@ -272,12 +330,30 @@ struct GatedRecParams {
     const float* a_bias;     // [C]
     const float* i_bias;     // [C]
     const float* lam;        // [C]
+    float* prepared;         // [3][T, C]: the decay less one, the input, the gate branch's activation
     SeqTables seq;
     StatePlace state;        // [C]
     void* out;               // [T, C]
     float gate_constant;
     int yx_stride, y_offset, channels, block_width, num_rows;
 };
+
+// First everything that does not depend on the state, for every (row, channel) side by side: the decay less one, the
+// gated input and the other branch's activation.  What is left for the pass along the tokens is two multiply-adds a step.
+__global__ void __launch_bounds__(128) gated_recurrence_prepare_kernel(GatedRecParams p) {
+    after_previous_kernel();
+    const int c = blockIdx.y * 128 + threadIdx.x;
+    const size_t row = blockIdx.x;
+    if (c >= p.channels) return;
+    const int bw = p.block_width, blk = c / bw, j = c - blk * bw;
+    const float* g_row = p.gates + ((size_t)blk * p.num_rows + row) * 2 * bw + j;
+    const float r = sigmoid_f(g_row[0] + p.a_bias[c]), in_gate = sigmoid_f(g_row[bw] + p.i_bias[c]);
+    const float log_a = -p.gate_constant * softplus_f(p.lam[c]) * r;
+    const size_t at = row * p.channels + c, plane = (size_t)p.num_rows * p.channels;
+    p.prepared[at] = expm1f(log_a);
+    p.prepared[plane + at] = sqrtf(-expm1f(2.0f * log_a)) * in_gate * p.u[at];          // 1 - a^2 without cancellation
+    p.prepared[2 * plane + at] = gelu_tanh_f(p.yx[row * p.yx_stride + p.y_offset + c] + (p.y_bias ? p.y_bias[c] : 0.f));
+}
 
 template <typename OutT>
 __global__ void __launch_bounds__(128) gated_recurrence_kernel(GatedRecParams p) {
@@ -287,31 +363,25 @@ __global__ void __launch_bounds__(128) gated_recurrence_kernel(GatedRecParams p)
     if (c >= p.channels) return;
     const int row0 = p.seq.cu_q_len[b], n_tok = p.seq.cu_q_len[b + 1] - row0;
     const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
-    const int bw = p.block_width, blk = c / bw, j = c - blk * bw;
-    const float* g_rows = p.gates + (size_t)blk * p.num_rows * 2 * bw + j;
-    const float y_bias = p.y_bias ? p.y_bias[c] : 0.f, a_bias = p.a_bias[c], i_bias = p.i_bias[c];
-    const float rate = p.gate_constant * softplus_f(p.lam[c]);
+    const size_t plane = (size_t)p.num_rows * p.channels;
     float S = state_at(p.state, slot, start & 1)[c];
     OutT* out = (OutT*)p.out;
-    for (int t0 = 0; t0 < n_tok; t0 += SCAN_TOKENS) {
-        const int count = min(SCAN_TOKENS, n_tok - t0);
-        float yv[SCAN_TOKENS], uv[SCAN_TOKENS], rv[SCAN_TOKENS], iv[SCAN_TOKENS];
+    for (int t0 = 0; t0 < n_tok; t0 += 2 * SCAN_TOKENS) {
+        const int count = min(2 * SCAN_TOKENS, n_tok - t0);
+        float am1[2 * SCAN_TOKENS], in[2 * SCAN_TOKENS], act[2 * SCAN_TOKENS];
 #pragma unroll
-        for (int t = 0; t < SCAN_TOKENS; ++t) {
+        for (int t = 0; t < 2 * SCAN_TOKENS; ++t) {
             const bool has = t < count;
-            const size_t row = (size_t)(row0 + t0 + t);
-            yv[t] = has ? p.yx[row * p.yx_stride + p.y_offset + c] : 0.f;
-            uv[t] = has ? p.u[row * p.channels + c] : 0.f;
-            rv[t] = has ? g_rows[row * 2 * bw] : 0.f;
-            iv[t] = has ? g_rows[row * 2 * bw + bw] : 0.f;
+            const size_t at = (size_t)(row0 + t0 + t) * p.channels + c;
+            am1[t] = has ? p.prepared[at] : 0.f;
+            in[t] = has ? p.prepared[plane + at] : 0.f;
+            act[t] = has ? p.prepared[2 * plane + at] : 0.f;
         }
 #pragma unroll
-        for (int t = 0; t < SCAN_TOKENS; ++t) {
+        for (int t = 0; t < 2 * SCAN_TOKENS; ++t) {
             if (t < count) {
-                const float r = sigmoid_f(rv[t] + a_bias), in_gate = sigmoid_f(iv[t] + i_bias);
-                const float log_a = -rate * r;
-                S = fmaf(expm1f(log_a), S, S) + sqrtf(-expm1f(2.0f * log_a)) * in_gate * uv[t];   // 1 - a^2 without cancellation
-                out[(size_t)(row0 + t0 + t) * p.channels + c] = from_f32<OutT>(S * gelu_tanh_f(yv[t] + y_bias));
+                S = fmaf(am1[t], S, S) + in[t];
+                out[(size_t)(row0 + t0 + t) * p.channels + c] = from_f32<OutT>(S * act[t]);
             }
         }
     }
@@ -320,18 +390,19 @@ __global__ void __launch_bounds__(128) gated_recurrence_kernel(GatedRecParams p)
 
 FRB_API int frb_gated_recurrence(const float* yx, int yx_stride, int y_offset, const float* y_bias, const float* u,
                                  const float* gates, const float* a_bias, const float* i_bias, const float* lam,
-                                 const int* seq_slot, const int* seq_start, const int* cu_q_len, float* state,
+                                 float* prepared, const int* seq_slot, const int* seq_start, const int* cu_q_len, float* state,
                                  long long copy_floats, long long state_offset, void* out, int out_dtype, int num_seqs,
                                  int num_rows, int channels, int block_width, float gate_constant, cudaStream_t stream) {
     if (num_seqs == 0) return 0;
-    FRB_CHECK_ARG(num_seqs <= 65535, "gated_recurrence: %d sequences exceed the grid", num_seqs);
+    FRB_CHECK_ARG(num_seqs <= 65535 && (channels + 127) / 128 <= 65535, "gated_recurrence: %d sequences exceed the grid", num_seqs);
     FRB_CHECK_ARG(block_width >= 1 && channels % block_width == 0, "gated_recurrence: %d channels in blocks of %d", channels,
                   block_width);
     GatedRecParams p;
     p.yx = yx; p.yx_stride = yx_stride; p.y_offset = y_offset; p.y_bias = y_bias; p.u = u; p.gates = gates; p.a_bias = a_bias;
-    p.i_bias = i_bias; p.lam = lam; p.seq = SeqTables{seq_slot, seq_start, cu_q_len};
+    p.i_bias = i_bias; p.lam = lam; p.prepared = prepared; p.seq = SeqTables{seq_slot, seq_start, cu_q_len};
     p.state = StatePlace{state, copy_floats, state_offset};
     p.out = out; p.gate_constant = gate_constant; p.channels = channels; p.block_width = block_width; p.num_rows = num_rows;
+    launch_dependent(gated_recurrence_prepare_kernel, dim3(num_rows, (channels + 127) / 128), dim3(128), 0, stream, p);
     dim3 grid((channels + 127) / 128, num_seqs);
     FRB_DISPATCH_DTYPE(out_dtype, OutT, {
         launch_dependent(gated_recurrence_kernel<OutT>, grid, dim3(128), 0, stream, p);
@@ -353,32 +424,37 @@ struct SsdParams {
     int proj_stride, z_offset, dt_offset, xbc_stride, b_offset, c_offset, heads, vdim, N, groups, parts, npad;
 };
 
-// A block takes (sequence, head, slice of 32 value columns); warp `part` keeps NREG rows of the state for each of its
-// lane's column.  Tokens go eight at a time: their B, C, x, step and decay are laid into shared memory by the whole
-// block, the eight steps run without a barrier, and the warps' shares of y are added in warp order.
-template <int NREG>
+// A block takes (sequence, head, slice of 32 VP value columns); warp `part` keeps NREG rows of the state for each of its
+// lane's VP columns (v = lane + 32 j).  Tokens go eight at a time: their B, C, x, step and decay are laid into shared
+// memory by the whole block, the eight steps run without a barrier (B and C of four rows come as one broadcast load
+// of 16 bytes each, for 12 VP multiply-adds), and the warps' shares of y are added in warp order.
+template <int NREG, int VP>
 __global__ void __launch_bounds__(512) state_space_scan_kernel(SsdParams p) {
-    extern __shared__ float sm[];
+    extern __shared__ __align__(16) float sm[];
     after_previous_kernel();
+    constexpr int COLS = 32 * VP;
     const int N = p.N, npad = p.npad, parts = p.parts, vdim = p.vdim;
     float* s_b = sm;                                   // [SCAN_TOKENS][npad]
     float* s_c = s_b + SCAN_TOKENS * npad;             // [SCAN_TOKENS][npad]
-    float* s_x = s_c + SCAN_TOKENS * npad;             // [SCAN_TOKENS][32]
-    float* s_dt = s_x + SCAN_TOKENS * 32;              // [SCAN_TOKENS]
+    float* s_x = s_c + SCAN_TOKENS * npad;             // [SCAN_TOKENS][COLS]
+    float* s_dt = s_x + SCAN_TOKENS * COLS;            // [SCAN_TOKENS]
     float* s_a = s_dt + SCAN_TOKENS;                   // [SCAN_TOKENS]
-    float* s_y = s_a + SCAN_TOKENS;                    // [SCAN_TOKENS][parts][32]
-    const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * 32;
+    float* s_y = s_a + SCAN_TOKENS;                    // [SCAN_TOKENS][parts][COLS]
+    const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * COLS;
     const int g = h / (p.heads / p.groups);
     const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
-    const int v = v0 + lane;
-    const bool col = v < vdim;
     const int row0 = p.seq.cu_q_len[b], n_tok = p.seq.cu_q_len[b + 1] - row0;
     const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
     const int n0 = part * NREG;
     const float* s_in = state_at(p.state, slot, start & 1) + (size_t)h * N * vdim;
-    float S[NREG];
+    float S[NREG][VP];
 #pragma unroll
-    for (int i = 0; i < NREG; ++i) S[i] = (col && n0 + i < N) ? s_in[(size_t)(n0 + i) * vdim + v] : 0.f;
+    for (int i = 0; i < NREG; ++i)
+#pragma unroll
+        for (int j = 0; j < VP; ++j) {
+            const int v = v0 + lane + 32 * j;
+            S[i][j] = (v < vdim && n0 + i < N) ? s_in[(size_t)(n0 + i) * vdim + v] : 0.f;
+        }
     const float dt_bias = p.dt_bias[h], rate = expf(p.a_log[h]), dskip = p.d[h];
     for (int i = threadIdx.x; i < 2 * SCAN_TOKENS * npad; i += blockDim.x) s_b[i] = 0.f;    // the padding stays zero
     for (int t0 = 0; t0 < n_tok; t0 += SCAN_TOKENS) {
@@ -390,35 +466,46 @@ __global__ void __launch_bounds__(512) state_space_scan_kernel(SsdParams p) {
             s_b[t * npad + n] = row[p.b_offset + g * N + n];
             s_c[t * npad + n] = row[p.c_offset + g * N + n];
         }
-        for (int i = threadIdx.x; i < count * 32; i += blockDim.x) {
-            const int t = i >> 5, l = i & 31;
+        for (int i = threadIdx.x; i < count * COLS; i += blockDim.x) {
+            const int t = i / COLS, l = i - t * COLS;
             s_x[i] = v0 + l < vdim ? p.xbc[(size_t)(row0 + t0 + t) * p.xbc_stride + h * vdim + v0 + l] : 0.f;
         }
         if (threadIdx.x < count) {
             const float step = softplus_f(p.proj[(size_t)(row0 + t0 + threadIdx.x) * p.proj_stride + p.dt_offset + h] + dt_bias);
             s_dt[threadIdx.x] = step;
-            s_a[threadIdx.x] = expm1f(-rate * step);               // the decay less one
+            s_a[threadIdx.x] = decay_less_one(-rate * step);
         }
         __syncthreads();
 #pragma unroll
         for (int t = 0; t < SCAN_TOKENS; ++t) {
             if (t < count) {
-                const float am1 = s_a[t], sx = s_dt[t] * s_x[t * 32 + lane];
-                float y = 0.f;
+                const float am1 = s_a[t], step = s_dt[t];
+                float sx[VP], y[VP];
 #pragma unroll
-                for (int i = 0; i < NREG; ++i) {
-                    S[i] = fmaf(am1, S[i], S[i]) + s_b[t * npad + n0 + i] * sx;
-                    y += S[i] * s_c[t * npad + n0 + i];
+                for (int j = 0; j < VP; ++j) { sx[j] = step * s_x[t * COLS + lane + 32 * j]; y[j] = 0.f; }
+#pragma unroll
+                for (int i = 0; i < NREG; i += 4) {
+                    const float4 b4 = *reinterpret_cast<const float4*>(s_b + t * npad + n0 + i);
+                    const float4 c4 = *reinterpret_cast<const float4*>(s_c + t * npad + n0 + i);
+                    const float bb[4] = {b4.x, b4.y, b4.z, b4.w}, cc[4] = {c4.x, c4.y, c4.z, c4.w};
+#pragma unroll
+                    for (int q = 0; q < 4; ++q)
+#pragma unroll
+                        for (int j = 0; j < VP; ++j) {
+                            S[i + q][j] = fmaf(am1, S[i + q][j], S[i + q][j]) + bb[q] * sx[j];
+                            y[j] = fmaf(S[i + q][j], cc[q], y[j]);
+                        }
                 }
-                s_y[(t * parts + part) * 32 + lane] = y;
+#pragma unroll
+                for (int j = 0; j < VP; ++j) s_y[(t * parts + part) * COLS + lane + 32 * j] = y[j];
             }
         }
         __syncthreads();
-        for (int i = threadIdx.x; i < count * 32; i += blockDim.x) {
-            const int t = i >> 5, l = i & 31;
+        for (int i = threadIdx.x; i < count * COLS; i += blockDim.x) {
+            const int t = i / COLS, l = i - t * COLS;
             if (v0 + l < vdim) {
                 float y = 0.f;
-                for (int q = 0; q < parts; ++q) y += s_y[(t * parts + q) * 32 + l];
+                for (int q = 0; q < parts; ++q) y += s_y[(t * parts + q) * COLS + l];
                 const size_t row = (size_t)(row0 + t0 + t);
                 const int channel = h * vdim + v0 + l;
                 const float z = p.proj[row * p.proj_stride + p.z_offset + channel];
@@ -426,12 +513,14 @@ __global__ void __launch_bounds__(512) state_space_scan_kernel(SsdParams p) {
             }
         }
     }
-    if (col) {
-        float* s_out = state_at(p.state, slot, (start + n_tok) & 1) + (size_t)h * N * vdim;
+    float* s_out = state_at(p.state, slot, (start + n_tok) & 1) + (size_t)h * N * vdim;
 #pragma unroll
-        for (int i = 0; i < NREG; ++i)
-            if (n0 + i < N) s_out[(size_t)(n0 + i) * vdim + v] = S[i];
-    }
+    for (int i = 0; i < NREG; ++i)
+#pragma unroll
+        for (int j = 0; j < VP; ++j) {
+            const int v = v0 + lane + 32 * j;
+            if (v < vdim && n0 + i < N) s_out[(size_t)(n0 + i) * vdim + v] = S[i][j];
+        }
 }
 
 FRB_API int frb_state_space_scan(const float* proj, int proj_stride, int z_offset, int dt_offset, const float* xbc,
@@ -442,9 +531,13 @@ FRB_API int frb_state_space_scan(const float* proj, int proj_stride, int z_offse
     if (num_seqs == 0) return 0;
     FRB_CHECK_ARG(groups >= 1 && heads % groups == 0, "state_space_scan: %d heads are not a multiple of %d groups", heads, groups);
     FRB_CHECK_ARG(N >= 1 && N <= 1024, "state_space_scan: a state of %d rows per head is outside 1..1024", N);
-    FRB_CHECK_ARG(heads <= 65535 && (vdim + 31) / 32 <= 65535, "state_space_scan: %d heads of %d exceed the grid", heads, vdim);
     int nreg = 8;
     while ((N + nreg - 1) / nreg > 16) nreg <<= 1;
+    // value columns a lane: as many as the head has (in 32s) while a thread's share of the state stays within 64 registers
+    int vp = vdim > 64 ? 4 : vdim > 32 ? 2 : 1;
+    while (vp > 1 && nreg * vp > 64) vp >>= 1;
+    const int cols = 32 * vp;
+    FRB_CHECK_ARG(heads <= 65535 && (vdim + cols - 1) / cols <= 65535, "state_space_scan: %d heads of %d exceed the grid", heads, vdim);
     SsdParams p;
     p.proj = proj; p.proj_stride = proj_stride; p.z_offset = z_offset; p.dt_offset = dt_offset; p.xbc = xbc;
     p.xbc_stride = xbc_stride; p.b_offset = b_offset; p.c_offset = c_offset; p.dt_bias = dt_bias; p.a_log = a_log; p.d = d;
@@ -453,14 +546,21 @@ FRB_API int frb_state_space_scan(const float* proj, int proj_stride, int z_offse
     p.out = out; p.heads = heads; p.vdim = vdim; p.N = N; p.groups = groups;
     p.parts = (N + nreg - 1) / nreg;
     p.npad = p.parts * nreg;
-    const size_t smem = ((size_t)2 * SCAN_TOKENS * p.npad + SCAN_TOKENS * 32 + 2 * SCAN_TOKENS + (size_t)SCAN_TOKENS * p.parts * 32)
+    const size_t smem = ((size_t)2 * SCAN_TOKENS * p.npad + SCAN_TOKENS * cols + 2 * SCAN_TOKENS + (size_t)SCAN_TOKENS * p.parts * cols)
                         * sizeof(float);
-    dim3 grid(num_seqs, heads, (vdim + 31) / 32);
+    dim3 grid(num_seqs, heads, (vdim + cols - 1) / cols);
     dim3 block(32 * p.parts);
-    if (nreg == 8) launch_dependent(state_space_scan_kernel<8>, grid, block, smem, stream, p);
-    else if (nreg == 16) launch_dependent(state_space_scan_kernel<16>, grid, block, smem, stream, p);
-    else if (nreg == 32) launch_dependent(state_space_scan_kernel<32>, grid, block, smem, stream, p);
-    else launch_dependent(state_space_scan_kernel<64>, grid, block, smem, stream, p);
+#define FRB_SSD(NREG, VP)                                                                                            \
+    do {                                                                                                             \
+        if (smem > 48 * 1024)                                                                                        \
+            cudaFuncSetAttribute(state_space_scan_kernel<NREG, VP>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_dependent(state_space_scan_kernel<NREG, VP>, grid, block, smem, stream, p);                           \
+    } while (0)
+    if (nreg == 8) { if (vp == 4) FRB_SSD(8, 4); else if (vp == 2) FRB_SSD(8, 2); else FRB_SSD(8, 1); }
+    else if (nreg == 16) { if (vp == 4) FRB_SSD(16, 4); else if (vp == 2) FRB_SSD(16, 2); else FRB_SSD(16, 1); }
+    else if (nreg == 32) { if (vp == 2) FRB_SSD(32, 2); else FRB_SSD(32, 1); }
+    else FRB_SSD(64, 1);
+#undef FRB_SSD
     FRB_RETURN_LAUNCH("state_space_scan");
 }
 

@@ -154,8 +154,9 @@ class GatedLinearRecurrence(_StateMixer):
             else:
                 gates = torch.bmm(per_block, self.w_gates.transpose(1, 2), out_dtype=torch.float32)
         out = ctx.buffer("gated_recurrence.y", (rows, c), self.dtype)
+        prepared = ctx.buffer("gated_recurrence.prepared", (3, rows, c), torch.float32)
         ops.gated_recurrence(yx, 0, w["y_bias"], u32, gates, w["a_gate_bias"], w["i_gate_bias"], w["lam"], ctx, line.state, 0,
-                             out, block_width=self.block_width, gate_constant=self.gate_constant)
+                             out, block_width=self.block_width, gate_constant=self.gate_constant, prepared=prepared)
         return linear(out, w["o_proj"])
 
 

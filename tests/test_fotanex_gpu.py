@@ -222,7 +222,8 @@ def test_gated_recurrence_with_decays_close_to_one():
         gates = np.concatenate([cut("r").reshape(rows, blocks, bw), cut("i").reshape(rows, blocks, bw)], axis=2).transpose(1, 0, 2)
         out = torch.empty((rows, width), dtype=torch.float32, device=DEV)
         ops().gated_recurrence(f32(yx), 4, f32(y_bias), f32(cut("u")), f32(gates), f32(a_bias), f32(i_bias), f32(lam), tables,
-                               state, 0, out, block_width=bw, gate_constant=8.0)
+                               state, 0, out, block_width=bw, gate_constant=8.0,
+                               prepared=torch.empty((3, rows, width), dtype=torch.float32, device=DEV))
         for b, s, m, (lo, hi) in zip(live, starts, sizes, tables.rows):
             got[b][s:s + m] = f64(out[lo:hi])
     for b in range(2):
