@@ -39,6 +39,9 @@ __device__ __forceinline__ float* state_at(const StatePlace& s, int slot, int co
 __device__ __forceinline__ float softplus_f(float v) { return fmaxf(v, 0.f) + log1pf(expf(-fabsf(v))); }
 __device__ __forceinline__ float sigmoid_f(float v) { return 1.0f / (1.0f + expf(-v)); }
 __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v)); }
+// silu for a result that is rounded to bfloat16 right away: the fast exponential and division (errors of 1e-6)
+template <typename OutT> __device__ __forceinline__ float silu_for(float v) { return silu_f(v); }
+template <> __device__ __forceinline__ float silu_for<bf16>(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
 // exp(x) - 1 for x <= 0 (a decay less one): a short series where the result is small, else the fast exponential,
 // whose error of a few 1e-7 of the decay then matters as little as the rounding of the state itself.
 __device__ __forceinline__ float decay_less_one(float x) {
@@ -270,7 +273,7 @@ __global__ void __launch_bounds__(SEL_BLOCK) selective_scan_kernel(SelScanParams
                 }
                 for (int o = 1; o < split; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
                 if (live && part == 0)
-                    out[(size_t)(row0 + t0 + t) * p.inner + c] = from_f32<OutT>((y + dskip * xv[t]) * silu_f(zv[t]));
+                    out[(size_t)(row0 + t0 + t) * p.inner + c] = from_f32<OutT>((y + dskip * xv[t]) * silu_for<OutT>(zv[t]));
             }
         }
     }
@@ -296,12 +299,16 @@ FRB_API int frb_selective_scan(const float* xz, int xz_stride, int z_offset, con
     if (num_seqs == 0) return 0;
     FRB_CHECK_ARG(N >= 1 && N <= 512, "selective_scan: a state of %d per channel is outside 1..512", N);
     FRB_CHECK_ARG(num_seqs <= 65535, "selective_scan: %d sequences exceed the grid", num_seqs);
-    // channels enough for the device with 16 elements a lane?  else 2 or 4 a lane, whichever leaves fewer lanes idle
-    int regs = 16;
-    if ((long long)num_seqs * inner * split_for(N, 16) < 128 * 1024 || split_for(N, 16) > 32) {
-        regs = split_for(N, 2) * 2 - N <= split_for(N, 4) * 4 - N && split_for(N, 2) <= 32 ? 2 : 4;
-        if (split_for(N, regs) > 32) regs = 16;
-    }
+    // The most elements a lane (16, 8, 4, 2) that still gives every SM a dozen warps: a lane's work per token beside the
+    // updates themselves (its loads, the additions across the lanes, the output) is shared by all of its elements.
+    static const int forced = [] { const char* v = getenv("FIELDRUN_B200_SCAN_ELEMENTS"); return v && v[0] ? atoi(v) : 0; }();
+    static const int sms = [] { int d = 0, n = 0; cudaGetDevice(&d); cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, d); return n; }();
+    int regs = 2;
+    for (int r = 16; r >= 2; r >>= 1)
+        if (split_for(N, r) <= 32 && ((long long)num_seqs * inner * split_for(N, r) / 32 >= 12LL * sms || r == 2)) { regs = r; break; }
+    if (forced == 2 || forced == 4 || forced == 8 || forced == 16) regs = forced;
+    while (split_for(N, regs) > 32) regs <<= 1;              // states of more than 64 elements need more than 2 a lane
+    FRB_CHECK_ARG(regs <= 16, "selective_scan: a state of %d per channel is more than the kernel takes", N);
     const int split = split_for(N, regs);
     SelScanParams p;
     p.xz = xz; p.xz_stride = xz_stride; p.z_offset = z_offset; p.x = x; p.low = low; p.low_stride = low_stride;
@@ -315,6 +322,7 @@ FRB_API int frb_selective_scan(const float* xz, int xz_stride, int z_offset, con
     FRB_DISPATCH_DTYPE(out_dtype, OutT, {
         if (regs == 2) launch_dependent(selective_scan_kernel<OutT, 2>, grid, dim3(SEL_BLOCK), smem, stream, p);
         else if (regs == 4) launch_dependent(selective_scan_kernel<OutT, 4>, grid, dim3(SEL_BLOCK), smem, stream, p);
+        else if (regs == 8) launch_dependent(selective_scan_kernel<OutT, 8>, grid, dim3(SEL_BLOCK), smem, stream, p);
         else launch_dependent(selective_scan_kernel<OutT, 16>, grid, dim3(SEL_BLOCK), smem, stream, p);
     });
     FRB_RETURN_LAUNCH("selective_scan");

@@ -353,7 +353,88 @@ def linear_attention(kind: str, launches: int) -> dict:
             "gbs": round(moved / ms / 1e6, 1)}
 
 
+class _Tables:
+    """A step's tables for the scans: sequences 0 .. n-1 from position 0."""
+
+    def __init__(self, lengths):
+        self.num_seqs = len(lengths)
+        self.seq_slot = torch.arange(len(lengths), dtype=torch.int32, device=DEV)
+        self.seq_start = torch.zeros(len(lengths), dtype=torch.int32, device=DEV)
+        self.cu_q_len = torch.tensor([0] + list(np.cumsum(lengths)), dtype=torch.int32, device=DEV)
+        self.tok_seq = torch.repeat_interleave(torch.arange(len(lengths), dtype=torch.int32, device=DEV),
+                                               torch.tensor(lengths, device=DEV)).to(torch.int32)
+
+
+def scans(kind: str, launches: int) -> dict:
+    """The recurrences of scans.cu alone, at the sizes of a model of width 2048, over four prompts of 2,048 tokens:
+    ``selective`` 4,096 channels with 16 state elements each, ``state_space`` 64 heads of 128 x 64, ``gated`` 2,048
+    channels, ``conv`` 4,096 channels with four taps.  Updates: state elements times tokens."""
+    lengths = [2048] * 4
+    tokens = sum(lengths)
+    tables = _Tables(lengths)
+    if kind == "selective":
+        inner, n, rank = 4096, 16, 128
+        xz = torch.randn(tokens, 2 * inner, device=DEV)
+        x = torch.randn(tokens, inner, device=DEV)
+        low = torch.randn(tokens, rank + 2 * n, device=DEV)
+        dt = torch.rand(tokens, inner, device=DEV) * 0.1
+        zero = torch.full((inner,), -20.0, device=DEV)               # softplus leaves a step size as it is, near enough
+        a_log, d = torch.randn(inner, n, device=DEV) * 0.5, torch.randn(inner, device=DEV)
+        state = torch.zeros(4, 2, inner * n, device=DEV)
+        out = torch.empty(tokens, inner, dtype=torch.bfloat16, device=DEV)
+
+        def launch():
+            ops.selective_scan(xz, inner, x, low, rank, rank + n, dt, zero, a_log, d, tables, state, 0, out)
+        updates, moved = tokens * inner * n, (xz.numel() // 2 + x.numel() + 2 * dt.numel() + low.numel()) * 4 + out.numel() * 2
+    elif kind == "state_space":
+        heads, vdim, n, groups = 64, 64, 128, 8
+        inner = heads * vdim
+        proj = torch.randn(tokens, inner + heads, device=DEV)
+        proj[:, inner:] -= 3.0
+        xbc = torch.randn(tokens, inner + 2 * groups * n, device=DEV) * 0.3
+        dt_bias, a_log, d = torch.zeros(heads, device=DEV), torch.zeros(heads, device=DEV), torch.ones(heads, device=DEV)
+        state = torch.zeros(4, 2, heads * n * vdim, device=DEV)
+        out = torch.empty(tokens, inner, device=DEV)
+
+        def launch():
+            ops.state_space_scan(proj, 0, inner, xbc, inner, inner + groups * n, dt_bias, a_log, d, tables, state, 0, out,
+                                 heads=heads, vdim=vdim, n=n, groups=groups)
+        updates, moved = tokens * heads * n * vdim, (proj.numel() + xbc.numel() + out.numel()) * 4
+    elif kind == "gated":
+        width, blocks = 2048, 16
+        yx = torch.randn(tokens, 2 * width, device=DEV)
+        u = torch.randn(tokens, width, device=DEV)
+        gates = torch.randn(blocks, tokens, 2 * width // blocks, device=DEV)
+        vec = torch.zeros(width, device=DEV)
+        state = torch.zeros(4, 2, width, device=DEV)
+        prepared = torch.empty(3, tokens, width, device=DEV)
+        out = torch.empty(tokens, width, dtype=torch.bfloat16, device=DEV)
+
+        def launch():
+            ops.gated_recurrence(yx, 0, vec, u, gates, vec, vec, vec, tables, state, 0, out, block_width=width // blocks,
+                                 gate_constant=8.0, prepared=prepared)
+        updates, moved = tokens * width, (yx.numel() // 2 + u.numel() + gates.numel() + 2 * prepared.numel()) * 4 + out.numel() * 2
+    else:
+        channels, taps = 4096, 4
+        rows = torch.randn(tokens, 2 * channels, device=DEV)
+        w, bias = torch.randn(channels, taps, device=DEV), torch.zeros(channels, device=DEV)
+        state = torch.zeros(4, 2, (taps - 1) * channels, device=DEV)
+        out32 = torch.empty(tokens, channels, device=DEV)
+        typed = torch.empty(tokens, channels, dtype=torch.bfloat16, device=DEV)
+
+        def launch():
+            ops.causal_conv(rows, 0, channels, w, bias, tables, state, 0, out32, typed, activation="silu")
+        updates, moved = tokens * channels * taps, rows.numel() // 2 * 4 + out32.numel() * 4 + typed.numel() * 2
+    ms = _time(launch, launches)
+    return {"case": f"scan_{kind}", "tokens": tokens, "ms": round(ms, 4), "updates_per_ns": round(updates / ms / 1e6, 1),
+            "gbs": round(moved / ms / 1e6, 1)}
+
+
 CASES = {
+    "scan_selective": lambda n: scans("selective", n),
+    "scan_state_space": lambda n: scans("state_space", n),
+    "scan_gated": lambda n: scans("gated", n),
+    "scan_conv": lambda n: scans("conv", n),
     "linear_attention_prefill": lambda n: linear_attention("prefill", n),
     "linear_attention_prefill_whole": lambda n: linear_attention("prefill_whole", n),
     "linear_attention_decode": lambda n: linear_attention("decode", n),
