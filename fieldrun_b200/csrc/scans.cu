@@ -42,11 +42,12 @@ __device__ __forceinline__ float silu_f(float v) { return v / (1.0f + expf(-v));
 // silu for a result that is rounded to bfloat16 right away: the fast exponential and division (errors of 1e-6)
 template <typename OutT> __device__ __forceinline__ float silu_for(float v) { return silu_f(v); }
 template <> __device__ __forceinline__ float silu_for<bf16>(float v) { return __fdividef(v, 1.0f + __expf(-v)); }
-// exp(x) - 1 for x <= 0 (a decay less one): a short series where the result is small, else the fast exponential,
-// whose error of a few 1e-7 of the decay then matters as little as the rounding of the state itself.
+// exp(x) - 1 for x <= 0 (a decay less one): four terms of the series where the result is small (the fifth is below
+// 1e-8 of it under 1/32), else the fast exponential, whose error of a few 1e-7 of the decay then matters as little as
+// the rounding of the state itself.
 __device__ __forceinline__ float decay_less_one(float x) {
-    const float series = x * fmaf(x * 0.5f, fmaf(x * (1.0f / 3.0f), fmaf(x * 0.25f, fmaf(x, 0.2f, 1.0f), 1.0f), 1.0f), 1.0f);
-    return x > -0.0625f ? series : __expf(x) - 1.0f;
+    const float series = x * fmaf(x, fmaf(x, fmaf(x, 1.0f / 24.0f, 1.0f / 6.0f), 0.5f), 1.0f);
+    return x > -0.03125f ? series : __expf(x) - 1.0f;
 }
 
 __device__ __forceinline__ float gelu_tanh_f(float v) {
@@ -432,22 +433,25 @@ struct SsdParams {
     int proj_stride, z_offset, dt_offset, xbc_stride, b_offset, c_offset, heads, vdim, N, groups, parts, npad;
 };
 
+__device__ __forceinline__ void copy_async4(float* dst, const float* src) {
+    asm volatile("cp.async.ca.shared.global [%0], [%1], 4;" ::"r"((uint32_t)__cvta_generic_to_shared(dst)), "l"(src) : "memory");
+}
+__device__ __forceinline__ void copies_wait() { asm volatile("cp.async.wait_all;" ::: "memory"); }
+
 // A block takes (sequence, head, slice of 32 VP value columns); warp `part` keeps NREG rows of the state for each of its
-// lane's VP columns (v = lane + 32 j).  Tokens go eight at a time: their B, C, x, step and decay are laid into shared
-// memory by the whole block, the eight steps run without a barrier (B and C of four rows come as one broadcast load
-// of 16 bytes each, for 12 VP multiply-adds), and the warps' shares of y are added in warp order.
+// lane's VP columns (v = lane + 32 j).  Tokens go eight at a time: their B, C, x, z, step and decay lie in one of two
+// buffers in shared memory, and while the eight steps of one buffer run (without a barrier; B and C of four rows come
+// as one broadcast load of 16 bytes each, for 12 VP multiply-adds) the rows of the next eight tokens are on their way
+// into the other (cp.async).  The warps' shares of y are added in warp order.
 template <int NREG, int VP>
 __global__ void __launch_bounds__(512) state_space_scan_kernel(SsdParams p) {
     extern __shared__ __align__(16) float sm[];
     after_previous_kernel();
     constexpr int COLS = 32 * VP;
     const int N = p.N, npad = p.npad, parts = p.parts, vdim = p.vdim;
-    float* s_b = sm;                                   // [SCAN_TOKENS][npad]
-    float* s_c = s_b + SCAN_TOKENS * npad;             // [SCAN_TOKENS][npad]
-    float* s_x = s_c + SCAN_TOKENS * npad;             // [SCAN_TOKENS][COLS]
-    float* s_dt = s_x + SCAN_TOKENS * COLS;            // [SCAN_TOKENS]
-    float* s_a = s_dt + SCAN_TOKENS;                   // [SCAN_TOKENS]
-    float* s_y = s_a + SCAN_TOKENS;                    // [SCAN_TOKENS][parts][COLS]
+    // one buffer: B [SCAN_TOKENS][npad], C [SCAN_TOKENS][npad], x [SCAN_TOKENS][COLS], z [SCAN_TOKENS][COLS], step and decay [SCAN_TOKENS] each
+    const int buffer_floats = 2 * SCAN_TOKENS * npad + 2 * SCAN_TOKENS * COLS + 2 * SCAN_TOKENS;
+    float* s_y = sm + 2 * buffer_floats;               // [SCAN_TOKENS][parts][COLS]
     const int b = blockIdx.x, h = blockIdx.y, v0 = blockIdx.z * COLS;
     const int g = h / (p.heads / p.groups);
     const int lane = threadIdx.x & 31, part = threadIdx.x >> 5;
@@ -464,26 +468,51 @@ __global__ void __launch_bounds__(512) state_space_scan_kernel(SsdParams p) {
             S[i][j] = (v < vdim && n0 + i < N) ? s_in[(size_t)(n0 + i) * vdim + v] : 0.f;
         }
     const float dt_bias = p.dt_bias[h], rate = expf(p.a_log[h]), dskip = p.d[h];
-    for (int i = threadIdx.x; i < 2 * SCAN_TOKENS * npad; i += blockDim.x) s_b[i] = 0.f;    // the padding stays zero
-    for (int t0 = 0; t0 < n_tok; t0 += SCAN_TOKENS) {
-        const int count = min(SCAN_TOKENS, n_tok - t0);
-        __syncthreads();
+    for (int i = threadIdx.x; i < 2 * buffer_floats; i += blockDim.x) sm[i] = 0.f;      // the padding stays zero
+    __syncthreads();
+    const int chunks = (n_tok + SCAN_TOKENS - 1) / SCAN_TOKENS;
+
+    // asks for the rows of chunk `k` into its buffer; the step and the decay are made here and stored directly
+    auto stage = [&](int k) {
+        float* s_b = sm + (k & 1) * buffer_floats;
+        float* s_c = s_b + SCAN_TOKENS * npad;
+        float* s_x = s_c + SCAN_TOKENS * npad;
+        float* s_z = s_x + SCAN_TOKENS * COLS;
+        float* s_dt = s_z + SCAN_TOKENS * COLS;
+        const int t0 = k * SCAN_TOKENS, count = min(SCAN_TOKENS, n_tok - t0);
         for (int i = threadIdx.x; i < count * N; i += blockDim.x) {
             const int t = i / N, n = i - t * N;
             const float* row = p.xbc + (size_t)(row0 + t0 + t) * p.xbc_stride;
-            s_b[t * npad + n] = row[p.b_offset + g * N + n];
-            s_c[t * npad + n] = row[p.c_offset + g * N + n];
+            copy_async4(s_b + t * npad + n, row + p.b_offset + g * N + n);
+            copy_async4(s_c + t * npad + n, row + p.c_offset + g * N + n);
         }
         for (int i = threadIdx.x; i < count * COLS; i += blockDim.x) {
             const int t = i / COLS, l = i - t * COLS;
-            s_x[i] = v0 + l < vdim ? p.xbc[(size_t)(row0 + t0 + t) * p.xbc_stride + h * vdim + v0 + l] : 0.f;
+            if (v0 + l < vdim) {
+                const size_t row = (size_t)(row0 + t0 + t);
+                copy_async4(s_x + i, p.xbc + row * p.xbc_stride + h * vdim + v0 + l);
+                copy_async4(s_z + i, p.proj + row * p.proj_stride + p.z_offset + h * vdim + v0 + l);
+            }
         }
         if (threadIdx.x < count) {
             const float step = softplus_f(p.proj[(size_t)(row0 + t0 + threadIdx.x) * p.proj_stride + p.dt_offset + h] + dt_bias);
             s_dt[threadIdx.x] = step;
-            s_a[threadIdx.x] = decay_less_one(-rate * step);
+            s_dt[SCAN_TOKENS + threadIdx.x] = decay_less_one(-rate * step);
         }
-        __syncthreads();
+    };
+
+    if (chunks > 0) stage(0);
+    for (int k = 0; k < chunks; ++k) {
+        const int t0 = k * SCAN_TOKENS, count = min(SCAN_TOKENS, n_tok - t0);
+        copies_wait();
+        __syncthreads();                               // chunk k lies in its buffer; nobody reads the other one any more
+        if (k + 1 < chunks) stage(k + 1);
+        const float* s_b = sm + (k & 1) * buffer_floats;
+        const float* s_c = s_b + SCAN_TOKENS * npad;
+        const float* s_x = s_c + SCAN_TOKENS * npad;
+        const float* s_z = s_x + SCAN_TOKENS * COLS;
+        const float* s_dt = s_z + SCAN_TOKENS * COLS;
+        const float* s_a = s_dt + SCAN_TOKENS;
 #pragma unroll
         for (int t = 0; t < SCAN_TOKENS; ++t) {
             if (t < count) {
@@ -514,10 +543,7 @@ __global__ void __launch_bounds__(512) state_space_scan_kernel(SsdParams p) {
             if (v0 + l < vdim) {
                 float y = 0.f;
                 for (int q = 0; q < parts; ++q) y += s_y[(t * parts + q) * COLS + l];
-                const size_t row = (size_t)(row0 + t0 + t);
-                const int channel = h * vdim + v0 + l;
-                const float z = p.proj[row * p.proj_stride + p.z_offset + channel];
-                p.out[row * (size_t)(p.heads * vdim) + channel] = (y + dskip * s_x[i]) * silu_f(z);
+                p.out[(size_t)(row0 + t0 + t) * (size_t)(p.heads * vdim) + h * vdim + v0 + l] = (y + dskip * s_x[i]) * silu_f(s_z[i]);
             }
         }
     }
@@ -554,8 +580,9 @@ FRB_API int frb_state_space_scan(const float* proj, int proj_stride, int z_offse
     p.out = out; p.heads = heads; p.vdim = vdim; p.N = N; p.groups = groups;
     p.parts = (N + nreg - 1) / nreg;
     p.npad = p.parts * nreg;
-    const size_t smem = ((size_t)2 * SCAN_TOKENS * p.npad + SCAN_TOKENS * cols + 2 * SCAN_TOKENS + (size_t)SCAN_TOKENS * p.parts * cols)
-                        * sizeof(float);
+    const size_t smem = (2 * ((size_t)2 * SCAN_TOKENS * p.npad + 2 * SCAN_TOKENS * cols + 2 * SCAN_TOKENS)
+                         + (size_t)SCAN_TOKENS * p.parts * cols) * sizeof(float);
+    FRB_CHECK_ARG(smem <= 200 * 1024, "state_space_scan: a state of %d rows needs more shared memory than a block has", N);
     dim3 grid(num_seqs, heads, (vdim + cols - 1) / cols);
     dim3 block(32 * p.parts);
 #define FRB_SSD(NREG, VP)                                                                                            \
