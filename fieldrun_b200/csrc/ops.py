@@ -34,7 +34,7 @@ _SIGNATURES = {
     "frb_concat_rows": "ppppiiii",
     "frb_add_row_vector": "pppii",
     "frb_head_gate": "pipiiii",
-    "frb_causal_conv": "piippppppppllppiiiii",
+    "frb_causal_conv": "piippppppppllppiiiiii",
     "frb_selective_scan": "piippiiipppppppllpiiii",
     "frb_softplus_bias": "ppii",
     "frb_gated_recurrence": "piipppppppppppllpiiiiif",
@@ -438,8 +438,8 @@ def causal_conv(rows_in: torch.Tensor, in_offset: int, channels: int, taps: torc
         raise KernelError("causal_conv: taps of another size than the channels, or an unknown activation")
     _call("frb_causal_conv", _ptr(rows_in), rows_in.shape[1], int(in_offset), _ptr(in_bias), _ptr(taps), _ptr(bias),
           _ptr(ctx.tok_seq), _ptr(ctx.seq_slot), _ptr(ctx.seq_start), _ptr(ctx.cu_q_len), *_state_place(state, state_offset),
-          _ptr(out32), _ptr(out_typed), _code(out_typed.dtype) if out_typed is not None else 0, rows_in.shape[0], channels,
-          taps.shape[1], CONV_ACTIVATIONS[activation])
+          _ptr(out32), _ptr(out_typed), _code(out_typed.dtype) if out_typed is not None else 0, rows_in.shape[0], ctx.num_seqs,
+          channels, taps.shape[1], CONV_ACTIVATIONS[activation])
 
 
 def selective_scan(xz: torch.Tensor, z_offset: int, x: torch.Tensor, low: torch.Tensor, b_offset: int, c_offset: int,

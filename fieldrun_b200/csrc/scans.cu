@@ -1,7 +1,8 @@
 // Recurrences over a float32 state per sequence, and the short causal convolution that stands in front of them.
 //
 //   causal_conv      out[t, c] = act(bias[c] + sum_k taps[c, k] * in[t - (K-1) + k, c]), the inputs before a step's first
-//                    token coming from the state (the last K-1 inputs of the sequence; zeros for a new sequence)
+//                    token coming from the state (the last K-1 inputs of the sequence; zeros for a new sequence); two
+//                    kernels: the rows that see only their own step, and each sequence's first rows with the state
 //   selective_scan   S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c x_c B_n;  y_c = sum_n S[c, n] C_n + D_c x_c;  y silu(z)
 //   gated_recurrence a = exp(-g r softplus(lam)),  S <- a S + sqrt(1 - a^2) i u,  out = S * act(y)    (per channel)
 //   state_space_scan per head: S <- exp(-exp(A_log) dt) S + dt B x^T (S is [N, vdim]);  y = S^T C + D x;  y silu(z)
@@ -76,90 +77,102 @@ __device__ __forceinline__ float conv_activation(float v, int activation) { retu
 
 #define CONV_ROWS 8          // rows of the step that one thread takes, one after the other, for its channel
 
-// A thread takes CONV_ROWS rows of the step for one channel and keeps the inputs it has seen in registers (right
-// aligned: the newest last), so that a row costs one load.  The row that is a sequence's first new one does all that
-// touches the state: the outputs of the first K-1 rows (the only ones that see inputs from before the step) and the
-// new state; rows 1 .. K-2 of a sequence are therefore skipped wherever they fall.
+// The rows that see only inputs of their own step (row i >= K-1 of its sequence).  A thread takes CONV_ROWS rows of the
+// step for one channel: the inputs of all of them (the rows themselves and the K-1 before the first) are asked for
+// before the first is used, and every row's window is a run of those registers.  Rows 0 .. K-2 of a sequence are the
+// other kernel's.
 template <typename OutT>
-__global__ void __launch_bounds__(128) causal_conv_kernel(ConvParams p) {
+__global__ void __launch_bounds__(128) causal_conv_rows_kernel(ConvParams p) {
     after_previous_kernel();
     const int c = blockIdx.y * 128 + threadIdx.x;
     if (c >= p.channels) return;
     const int K = p.taps_count;
-    float w[CONV_MAX_TAPS];                    // right aligned like the window: w[MAX - K + k] is tap k
+    const int r_begin = blockIdx.x * p.rows_per_thread, r_end = min(p.num_rows, r_begin + p.rows_per_thread);
+    const float in_bias = p.in_bias ? p.in_bias[c] : 0.f;
+    const float* in = p.in + p.in_offset + c;
+    // vals[m]: the input of row r_begin - (MAX - 1) + m; a row's window is right aligned, the newest last
+    float vals[CONV_ROWS + CONV_MAX_TAPS - 1];
+#pragma unroll
+    for (int m = 0; m < CONV_ROWS + CONV_MAX_TAPS - 1; ++m) {
+        const int r = r_begin - (CONV_MAX_TAPS - 1) + m;
+        vals[m] = (m >= CONV_MAX_TAPS - K && r >= 0 && r < r_end) ? in[(size_t)r * p.in_stride] + in_bias : 0.f;
+    }
+    float w[CONV_MAX_TAPS];                    // right aligned like the windows: w[MAX - K + k] is tap k
 #pragma unroll
     for (int j = 0; j < CONV_MAX_TAPS; ++j) w[j] = j >= CONV_MAX_TAPS - K ? p.taps[(size_t)c * K + j - (CONV_MAX_TAPS - K)] : 0.f;
+    const float bias = p.bias ? p.bias[c] : 0.f;
+    OutT* typed = (OutT*)p.out_typed;
+    // most threads' rows lie in one sequence: its tables are then looked up once, not row by row
+    const int b_first = p.tok_seq[r_begin], b_last = p.tok_seq[r_end - 1];
+    const int row0_first = p.seq.cu_q_len[b_first];
+    const bool one_sequence = b_first == b_last;
+#pragma unroll
+    for (int q = 0; q < CONV_ROWS; ++q) {
+        const int r = r_begin + q;
+        if (r < r_end) {
+            const int row0 = one_sequence ? row0_first : p.seq.cu_q_len[p.tok_seq[r]];
+            if (r - row0 >= K - 1) {
+                float acc = bias;
+#pragma unroll
+                for (int j = 0; j < CONV_MAX_TAPS; ++j) acc = fmaf(w[j], vals[q + j], acc);
+                acc = conv_activation(acc, p.activation);
+                p.out32[(size_t)r * p.channels + c] = acc;
+                if (typed) typed[(size_t)r * p.channels + c] = from_f32<OutT>(acc);
+            }
+        }
+    }
+}
+
+// A thread per (sequence, channel) does all that touches the state: the outputs of the sequence's first K-1 new rows
+// (the only ones that see inputs from before the step) and the new state.  It reads the old state before it writes.
+template <typename OutT>
+__global__ void __launch_bounds__(128) causal_conv_heads_kernel(ConvParams p) {
+    after_previous_kernel();
+    const int c = blockIdx.y * 128 + threadIdx.x;
+    const int b = blockIdx.x;
+    if (c >= p.channels) return;
+    const int K = p.taps_count;
     const float bias = p.bias ? p.bias[c] : 0.f, in_bias = p.in_bias ? p.in_bias[c] : 0.f;
     const float* in = p.in + p.in_offset + c;
     OutT* typed = (OutT*)p.out_typed;
-    float win[CONV_MAX_TAPS];
-    bool have = false;                         // win holds the inputs of the row before this one
-    const int r_end = min(p.num_rows, (int)(blockIdx.x + 1) * p.rows_per_thread);
-    for (int r = blockIdx.x * p.rows_per_thread; r < r_end; ++r) {
-        const int b = p.tok_seq[r];
-        const int row0 = p.seq.cu_q_len[b];
-        const int i = r - row0;
-        if (i >= K - 1) {
-            if (have) {
+    const int row0 = p.seq.cu_q_len[b], n = p.seq.cu_q_len[b + 1] - row0;
+    const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
+    const float* old_tail = state_at(p.state, slot, start & 1);
+    float* new_tail = state_at(p.state, slot, (start + n) & 1);
+    // hist[m], m < K-1: the inputs before the step; hist[MAX + j]: the step's own input j, for the rows handled here
+    float hist[2 * CONV_MAX_TAPS];
 #pragma unroll
-                for (int j = 0; j < CONV_MAX_TAPS - 1; ++j) win[j] = win[j + 1];
-                win[CONV_MAX_TAPS - 1] = in[(size_t)r * p.in_stride] + in_bias;
-            } else {
+    for (int m = 0; m < CONV_MAX_TAPS; ++m) hist[m] = m < K - 1 ? old_tail[(size_t)m * p.channels + c] : 0.f;
+    const int own = min(n, K - 1);
 #pragma unroll
-                for (int j = 0; j < CONV_MAX_TAPS; ++j)
-                    win[j] = j >= CONV_MAX_TAPS - K ? in[(size_t)(r - (CONV_MAX_TAPS - 1 - j)) * p.in_stride] + in_bias : 0.f;
-                have = true;
-            }
-            float acc = bias;
-#pragma unroll
-            for (int j = 0; j < CONV_MAX_TAPS; ++j) acc = fmaf(w[j], win[j], acc);
-            acc = conv_activation(acc, p.activation);
-            p.out32[(size_t)r * p.channels + c] = acc;
-            if (typed) typed[(size_t)r * p.channels + c] = from_f32<OutT>(acc);
-            continue;                           // with K == 1 there is no state and every row ends here
+    for (int j = 0; j < CONV_MAX_TAPS; ++j)
+        hist[CONV_MAX_TAPS + j] = j < own ? in[(size_t)(row0 + j) * p.in_stride] + in_bias : 0.f;
+    for (int j = 0; j < own; ++j) {
+        float acc = bias;
+        for (int k = 0; k < K; ++k) {
+            const int at = j - (K - 1) + k;                       // index among the step's inputs; negative: before it
+            const float v = at >= 0 ? hist[CONV_MAX_TAPS + at] : hist[K - 1 + at];
+            acc = fmaf(p.taps[(size_t)c * K + k], v, acc);
         }
-        have = false;
-        if (i > 0) continue;
-        // i == 0
-        const int n = p.seq.cu_q_len[b + 1] - row0;
-        const int start = p.seq.seq_start[b], slot = p.seq.seq_slot[b];
-        const float* old_tail = state_at(p.state, slot, start & 1);
-        float* new_tail = state_at(p.state, slot, (start + n) & 1);
-        // hist[m], m < K-1: the inputs before the step; hist[MAX + j]: the step's own input j, for the rows handled here
-        float hist[2 * CONV_MAX_TAPS];
-#pragma unroll
-        for (int m = 0; m < CONV_MAX_TAPS; ++m) hist[m] = m < K - 1 ? old_tail[(size_t)m * p.channels + c] : 0.f;
-        const int own = min(n, K - 1);
-#pragma unroll
-        for (int j = 0; j < CONV_MAX_TAPS; ++j)
-            hist[CONV_MAX_TAPS + j] = j < own ? in[(size_t)(row0 + j) * p.in_stride] + in_bias : 0.f;
-        for (int j = 0; j < own; ++j) {
-            float acc = bias;
-            for (int k = 0; k < K; ++k) {
-                const int at = j - (K - 1) + k;                       // index among the step's inputs; negative: before it
-                const float v = at >= 0 ? hist[CONV_MAX_TAPS + at] : hist[K - 1 + at];
-                acc = fmaf(p.taps[(size_t)c * K + k], v, acc);
-            }
-            acc = conv_activation(acc, p.activation);
-            p.out32[(size_t)(row0 + j) * p.channels + c] = acc;
-            if (typed) typed[(size_t)(row0 + j) * p.channels + c] = from_f32<OutT>(acc);
-        }
-        for (int m = 0; m < K - 1; ++m) {
-            const int at = n - (K - 1) + m;                           // the step's input that becomes entry m of the new state
-            float v;
-            if (at < 0) v = hist[K - 1 + at];
-            else if (at < own) v = hist[CONV_MAX_TAPS + at];
-            else v = in[(size_t)(row0 + at) * p.in_stride] + in_bias;
-            new_tail[(size_t)m * p.channels + c] = v;
-        }
+        acc = conv_activation(acc, p.activation);
+        p.out32[(size_t)(row0 + j) * p.channels + c] = acc;
+        if (typed) typed[(size_t)(row0 + j) * p.channels + c] = from_f32<OutT>(acc);
+    }
+    for (int m = 0; m < K - 1; ++m) {
+        const int at = n - (K - 1) + m;                           // the step's input that becomes entry m of the new state
+        float v;
+        if (at < 0) v = hist[K - 1 + at];
+        else if (at < own) v = hist[CONV_MAX_TAPS + at];
+        else v = in[(size_t)(row0 + at) * p.in_stride] + in_bias;
+        new_tail[(size_t)m * p.channels + c] = v;
     }
 }
 
 FRB_API int frb_causal_conv(const float* in, int in_stride, int in_offset, const float* in_bias, const float* taps,
                             const float* bias, const int* tok_seq, const int* seq_slot, const int* seq_start,
                             const int* cu_q_len, float* state, long long copy_floats, long long state_offset, float* out32,
-                            void* out_typed, int typed_dtype, int num_rows, int channels, int taps_count, int activation,
-                            cudaStream_t stream) {
+                            void* out_typed, int typed_dtype, int num_rows, int num_seqs, int channels, int taps_count,
+                            int activation, cudaStream_t stream) {
     if (num_rows == 0) return 0;
     FRB_CHECK_ARG(taps_count >= 1 && taps_count <= CONV_MAX_TAPS, "causal_conv: %d taps are outside 1..%d", taps_count,
                   CONV_MAX_TAPS);
@@ -172,8 +185,11 @@ FRB_API int frb_causal_conv(const float* in, int in_stride, int in_offset, const
     FRB_CHECK_ARG((channels + 127) / 128 <= 65535, "causal_conv: %d channels exceed the grid", channels);
     p.rows_per_thread = num_rows >= 2048 ? CONV_ROWS : 1;
     dim3 grid((num_rows + p.rows_per_thread - 1) / p.rows_per_thread, (channels + 127) / 128);
+    dim3 heads(num_seqs, (channels + 127) / 128);
     FRB_DISPATCH_DTYPE(typed_dtype, OutT, {
-        launch_dependent(causal_conv_kernel<OutT>, grid, dim3(128), 0, stream, p);
+        // one token a sequence: no row sees only its own step (unless there is one tap, and then no state)
+        if (taps_count == 1 || num_rows > num_seqs) launch_dependent(causal_conv_rows_kernel<OutT>, grid, dim3(128), 0, stream, p);
+        if (taps_count > 1) launch_dependent(causal_conv_heads_kernel<OutT>, heads, dim3(128), 0, stream, p);
     });
     FRB_RETURN_LAUNCH("causal_conv");
 }
@@ -183,19 +199,19 @@ FRB_API int frb_causal_conv(const float* in, int in_stride, int in_offset, const
 #define SEL_BLOCK 128
 
 // x <- softplus(x + bias), row by row: the step sizes of the selective scan, made once for all the lanes that share them
-__global__ void __launch_bounds__(256) softplus_bias_kernel(float* __restrict__ x, const float* __restrict__ bias, int width) {
+__global__ void __launch_bounds__(256) softplus_bias_kernel(float* __restrict__ x, const float* __restrict__ bias, int num_rows,
+                                                            int width) {
     after_previous_kernel();
-    const int c = blockIdx.y * 256 + threadIdx.x;
-    if (c < width) {
-        const size_t i = (size_t)blockIdx.x * width + c;
-        x[i] = softplus_f(x[i] + bias[c]);
-    }
+    for (int row = blockIdx.x; row < num_rows; row += gridDim.x)
+        for (int c = threadIdx.x; c < width; c += 256) {
+            const size_t i = (size_t)row * width + c;
+            x[i] = softplus_f(x[i] + bias[c]);
+        }
 }
 
 FRB_API int frb_softplus_bias(float* x, const float* bias, int num_rows, int width, cudaStream_t stream) {
     if (num_rows == 0) return 0;
-    FRB_CHECK_ARG((width + 255) / 256 <= 65535, "softplus_bias: rows of %d exceed the grid", width);
-    launch_dependent(softplus_bias_kernel, dim3(num_rows, (width + 255) / 256), dim3(256), 0, stream, x, bias, width);
+    launch_dependent(softplus_bias_kernel, dim3(num_rows < 2368 ? num_rows : 2368), dim3(256), 0, stream, x, bias, num_rows, width);
     FRB_RETURN_LAUNCH("softplus_bias");
 }
 

@@ -10,6 +10,7 @@
 #include "common.cuh"
 
 #define ROW_BLOCK 256
+#define DYT_MAX_ROWS 64      // the most weighted rows that the norm sums for a token
 
 struct DytParams {
     float* x;                 // [T, width]
@@ -29,11 +30,20 @@ struct DytParams {
 
 template <typename OutT>
 __global__ void __launch_bounds__(ROW_BLOCK) dyt_norm_kernel(DytParams p) {
+    __shared__ float s_weight[DYT_MAX_ROWS];
+    __shared__ int s_row[DYT_MAX_ROWS];
     after_previous_kernel();
     const int r = blockIdx.x;
     const int src = p.rows ? p.rows[r] : r;
     const size_t base = (size_t)src * p.width, obase = (size_t)r * p.width;
     const float a1 = *p.alpha1, a2 = p.w2 ? *p.alpha2 : 0.f;
+    if (p.y) {                                          // the row's experts: weights and rows once, not per element
+        if (threadIdx.x < p.top_k) {
+            s_weight[threadIdx.x] = p.ew[(size_t)src * p.top_k + threadIdx.x];
+            s_row[threadIdx.x] = p.rowmap[(size_t)src * p.top_k + threadIdx.x];
+        }
+        __syncthreads();
+    }
     for (int i = threadIdx.x; i < p.width; i += ROW_BLOCK) {
         float v = p.x[base + i];
         float d = 0.f;
@@ -42,8 +52,7 @@ __global__ void __launch_bounds__(ROW_BLOCK) dyt_norm_kernel(DytParams p) {
         if (p.delta1) { d += p.delta1[base + i]; any = true; }
         if (p.y) {
             float e = 0.f;
-            for (int k = 0; k < p.top_k; ++k)
-                e += p.ew[(size_t)src * p.top_k + k] * p.y[(size_t)p.rowmap[(size_t)src * p.top_k + k] * p.width + i];
+            for (int k = 0; k < p.top_k; ++k) e += s_weight[k] * p.y[(size_t)s_row[k] * p.width + i];
             d += e;
             any = true;
         }
@@ -66,6 +75,7 @@ FRB_API int frb_dyt_norm(float* x, const float* delta0, const float* delta1, con
                          float* out2_32, int out_dtype, int num_rows, int width, int write_back, cudaStream_t stream) {
     if (num_rows == 0) return 0;
     FRB_CHECK_ARG(!(rows && write_back), "dyt_norm: chosen rows cannot be stored back");
+    FRB_CHECK_ARG(!y || (top_k >= 1 && top_k <= DYT_MAX_ROWS), "dyt_norm: %d weighted rows a token are outside 1..%d", top_k, DYT_MAX_ROWS);
     DytParams p;
     p.x = x; p.delta0 = delta0; p.delta1 = delta1; p.y = y; p.ew = ew; p.rowmap = rowmap; p.rows = rows;
     p.w1 = w1; p.b1 = b1; p.alpha1 = alpha1; p.out1 = out1; p.w2 = w2; p.b2 = b2; p.alpha2 = alpha2; p.out2 = out2;
