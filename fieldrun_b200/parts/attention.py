@@ -85,6 +85,8 @@ class GQAAttention(Mixer):
         self.position = build_position(a.get("position"))
         if self.position is not None and self.position.rotary_dim > self.head_dim:
             raise ValueError(f"rotary_dim {self.position.rotary_dim} exceeds head_dim {self.head_dim}")
+        if not (dtype == torch.bfloat16 and self.value_dim == self.head_dim and self.head_dim in ops.MMA_HEAD_DIMS):
+            self.kernel_groups = ("common", "streams")          # the tensor-core kernels take none of this part's steps
         self.q_width = self.num_heads * self.head_dim
         self.kv_width = self.num_kv_heads * self.head_dim
         self.v_width = self.num_kv_heads * self.value_dim

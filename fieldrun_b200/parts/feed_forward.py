@@ -58,6 +58,8 @@ class RoutedExperts(FeedForward):
         self.routed_scale = float(a.get("routed_scale", 1.0))
         if not 1 <= self.top_k <= self.num_experts:
             raise ValueError(f"top_k {self.top_k} is outside 1..{self.num_experts} experts")
+        if not (dtype == torch.bfloat16 and self.hidden_size % 128 == 0 and self.expert_width % 128 == 0):
+            self.kernel_groups = ("common", "streams", "experts")      # sizes the tcgen05 products never take
         self.router: Optional[torch.Tensor] = None
         self.bias: Optional[torch.Tensor] = None
         self.w13: Optional[torch.Tensor] = None
