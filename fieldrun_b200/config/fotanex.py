@@ -72,11 +72,13 @@ class FotanexChunkAttention:
     dim: int
     vdim: int
     scale: float
-    chunk: int
+    chunk: Optional[int]                  # None: a file without a mask; every earlier key is seen
 
     def to_json(self) -> dict[str, Any]:
-        return {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale,
-                "mask": {"size": self.chunk}}
+        out: dict[str, Any] = {"heads": self.heads, "kv_heads": self.kv_heads, "dim": self.dim, "vdim": self.vdim, "scale": self.scale}
+        if self.chunk is not None:
+            out["mask"] = {"size": self.chunk}
+        return out
 
 
 @dataclass(frozen=True)
@@ -162,10 +164,12 @@ def _parallel(raw: Mapping[str, Any], where: str) -> FotanexParallel:
     if heads % kv_heads:
         raise ConfigError(f"{where}.left: {heads} heads are not a multiple of {kv_heads} kv_heads")
     dim = a.integer("dim", minimum=1)
-    _unknown(_object(left.get("mask"), where + ".left.mask"), {"size"}, where + ".left.mask")
+    chunk = None
+    if left.get("mask") is not None:
+        _unknown(_object(left["mask"], where + ".left.mask"), {"size"}, where + ".left.mask")
+        chunk = a.integer("mask.size", minimum=1)
     attention = FotanexChunkAttention(heads, kv_heads, dim, a.integer("vdim", default=dim, minimum=1),
-                                      a.real("scale", default=float(dim) ** -0.5, positive=True),
-                                      a.integer("mask.size", minimum=1))
+                                      a.real("scale", default=float(dim) ** -0.5, positive=True), chunk)
     s = KeyReader(right, where + ".right")
     scan = FotanexScan(s.integer("inner", minimum=1), s.integer("state", minimum=1), s.integer("dt_rank", minimum=1),
                        s.integer("conv", minimum=1))

@@ -34,6 +34,9 @@ def test_impossible_configurations_are_refused_by_key():
                               (("norm",), {"eps": 0}, "eps"), (("vocab",), "many", "vocab")):
         with pytest.raises(ConfigError, match=word):
             FotanexConfig.from_dict(changed(path, value))
+    plain = changed(("layers", 1, "mixer"), {"left": {"heads": 2, "dim": 8}, "right": dict(CONFIG_A["layers"][1]["mixer"]["right"])})
+    left = FotanexConfig.from_dict(plain).layers[1].mixer.left
+    assert (left.kv_heads, left.vdim, left.chunk, left.scale) == (2, 8, None, 8 ** -0.5)      # what a file may leave out
     raw = changed(("layers", 1, "mlp"), {"kind": "moe", "expert": {"ff": 8}, "router": {"experts": 2, "top": 3}})
     with pytest.raises(ConfigError, match="top"):
         FotanexConfig.from_dict(raw)
